@@ -1,0 +1,174 @@
+/*
+ * lf_sm100.h - C ABI of liblf_sm100.so: hand-written sm_100a (B200) kernels for the fused
+ * attention hot path that the loopfuse compiler generates.
+ *
+ * Every entry point takes plain device pointers, element strides and sizes; nothing in
+ * the signatures depends on PyTorch. Pointers are borrowed (never freed by the library).
+ * All launches are asynchronous on the CUDA stream passed in (a cudaStream_t carried as
+ * void*; NULL = the legacy default stream). Return value: LF_OK, or a negative LfStatus
+ * for argument / launch errors detected on the host. Device-side problems (a bounded wait
+ * that ran out, a page id outside the pool) are written to the optional `status` device
+ * word as a positive code; the kernels never trap.
+ *
+ * Reference interface each entry replaces (paths inside tomatillos/loopfuse):
+ *   lf_prefill_bf16        the generated launcher + kernel for prefill graphs:
+ *                          loopfuse/codegen.py:215-298 (launch_kernel_0), :454-998 (body);
+ *                          called from loopfuse/torch_backend/interface.py:640-644.
+ *   lf_decode_bf16         same generator, M==1 special case loopfuse/codegen.py:661-663.
+ *   lf_decode_paged_bf16   same, with the two-level paged load loopfuse/codegen.py:738-872
+ *                          (op: loopfuse/torch_backend/__init__.py:46-63).
+ *   lf_combine_f32         no reference counterpart as a separate kernel: the reference runs
+ *                          the whole KV loop in one program (README.md:117 lists split-k as
+ *                          missing); this merges split-KV partial results.
+ *   lf_paged_gather_bf16   the eager gather buffer[block_table]
+ *                          (loopfuse/torch_backend/__init__.py:46-56), used to check page
+ *                          indexing bit for bit.
+ *   lf_skip_range          the loop-range rewrite of the sparsity pass,
+ *                          loopfuse/compiler/passes/skip_loop_iterations.py:343-376.
+ */
+#ifndef LF_SM100_H_
+#define LF_SM100_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LF_ABI_VERSION 1
+
+typedef enum {
+  LF_OK = 0,
+  LF_ERR_INVALID_ARG = -1,   /* NULL pointer, bad size, unsupported head dim ...            */
+  LF_ERR_UNSUPPORTED = -2,   /* valid request that this build has no kernel for             */
+  LF_ERR_ALIGNMENT = -3,     /* pointer / stride not aligned as the kernels require         */
+  LF_ERR_WORKSPACE = -4,     /* split-KV workspace missing or too small                     */
+  LF_ERR_CUDA = -5,          /* a CUDA runtime / driver call failed (see lf_last_cuda_error) */
+  LF_ERR_NO_DEVICE = -6,     /* no sm_100 device is current                                 */
+  LF_ERR_TOO_LARGE = -7      /* size beyond a fixed limit of the entry point                */
+} LfStatus;
+
+/* Codes the kernels write to the `status` device word (0 = nothing happened). */
+#define LF_DEV_OK 0
+#define LF_DEV_TIMEOUT 1        /* a bounded mbarrier wait gave up; low bits say which      */
+#define LF_DEV_BAD_PAGE 2       /* block_table entry outside [0, n_pages)                   */
+
+/* Mask kinds (what the capture layer deduces from loopfuse::causal_mask / sliding_mask). */
+#define LF_MASK_NONE 0
+#define LF_MASK_CAUSAL 1          /* keep j <= i + causal_offset                             */
+#define LF_MASK_CAUSAL_WINDOW 2   /* keep i + off - (window-1) <= j <= i + off               */
+
+/* Score-mod opcodes: applied in order to s = scale * (q . k) before the mask. */
+#define LF_MOD_MUL 1     /* s *= arg   */
+#define LF_MOD_ADD 2     /* s += arg   */
+#define LF_MOD_TANH 3
+#define LF_MOD_EXP 4
+#define LF_MOD_EXP2 5
+#define LF_MOD_SIN 6
+#define LF_MOD_COS 7
+#define LF_MOD_RELU 8
+#define LF_MOD_SQUARE 9
+#define LF_MOD_DIV 10    /* s /= arg   */
+#define LF_MAX_MODS 8
+
+/* Prefill tile shape the sm_100a kernel uses; skip ranges are defined on it. */
+#define LF_PREFILL_TILE_Q 128
+#define LF_PREFILL_TILE_K 128
+
+typedef struct {
+  const void* q;      /* bf16 [B, Hq,  Sq,  D], innermost stride 1 */
+  const void* k;      /* bf16 [B, Hkv, Skv, D] */
+  const void* v;      /* bf16 [B, Hkv, Skv, D] */
+  void* out;          /* bf16 [B, Hq,  Sq,  D] */
+  int32_t B, Hq, Hkv, Sq, Skv, D;   /* D in {64, 128}; Hq % Hkv == 0 */
+  int64_t q_stride[3];  /* element strides of dims (b, h, s) */
+  int64_t k_stride[3];
+  int64_t v_stride[3];
+  int64_t o_stride[3];
+  float scale;          /* first multiplier of q.k (D^-0.5 in the usual case) */
+  int32_t n_mod;        /* 0..LF_MAX_MODS */
+  int32_t mod_op[LF_MAX_MODS];
+  float mod_arg[LF_MAX_MODS];
+  int32_t mask_kind;    /* LF_MASK_* */
+  int32_t window;       /* for LF_MASK_CAUSAL_WINDOW */
+  int32_t causal_offset;/* 0 for square scores */
+  int32_t* status;      /* optional device word */
+  int32_t* dbg_ranges;  /* optional device int32 [B*Hq*ceil(Sq/128)*2]: the (lo,hi) KV-tile
+                           range each q-tile actually iterated, for the bit-exact check */
+} LfPrefillArgs;
+
+typedef struct {
+  const void* q;        /* bf16 [B, Hkv, G, D]: the G query heads that share a kv head */
+  const void* k;        /* dense: bf16 [B, Hkv, Skv, D]. paged: pool [n_pages, page_size, Hkv, D] */
+  const void* v;
+  void* out;            /* bf16 [B, Hkv, G, D] */
+  int32_t B, Hkv, G, Skv, D;   /* D in {64, 128}; G in {1, 2, 4, 8} */
+  int64_t q_stride[3];  /* (b, hkv, g) */
+  int64_t o_stride[3];
+  int64_t k_stride[3];  /* dense: (b, hkv, s). paged: (page, slot, hkv) */
+  int64_t v_stride[3];
+  float scale;
+  int32_t n_mod;
+  int32_t mod_op[LF_MAX_MODS];
+  float mod_arg[LF_MAX_MODS];
+  /* paged only */
+  const int32_t* block_table;   /* int32 [B, ceil(Skv/page_size)]: pages of K (and of V) */
+  const int32_t* block_table_v; /* pages of V when they differ from K's; NULL = same table */
+  int64_t bt_stride;            /* elements between rows of block_table */
+  int32_t page_size;
+  int32_t n_pages;
+  /* split-KV */
+  int32_t splits;               /* >= 1; 0 = let the library choose */
+  void* workspace;              /* device, >= lf_decode_workspace_bytes(...) when splits != 1 */
+  size_t workspace_bytes;
+  int32_t* status;              /* optional device word */
+} LfDecodeArgs;
+
+typedef struct {
+  int32_t abi_version;
+  int32_t device;         /* current CUDA device ordinal */
+  int32_t cc_major, cc_minor;
+  int32_t sm_count;
+  int32_t max_smem_optin; /* bytes */
+  int64_t total_mem;
+} LfDeviceInfo;
+
+/* Fill *info for the current device. */
+int lf_query(LfDeviceInfo* info);
+
+const char* lf_strerror(int status);
+/* Text of the last CUDA error seen by this thread inside the library ("" if none). */
+const char* lf_last_cuda_error(void);
+
+/* Prefill attention: out = softmax(mask(mod(scale * q k^T))) v, online softmax, tcgen05 MMA. */
+int lf_prefill_bf16(const LfPrefillArgs* args, void* stream);
+
+/* KV-tile range [lo, hi) that q-tile `iq` must visit; the same integers the kernel uses. */
+void lf_skip_range(int32_t mask_kind, int32_t window, int32_t causal_offset, int32_t Sq,
+                   int32_t Skv, int32_t tile_q, int32_t tile_k, int32_t iq, int32_t* lo,
+                   int32_t* hi);
+
+/* Decode attention (Sq == 1 per head, G grouped heads per kv head), split over KV. */
+int lf_decode_bf16(const LfDecodeArgs* args, void* stream);
+int lf_decode_paged_bf16(const LfDecodeArgs* args, void* stream);
+/* Split count the library picks for splits == 0, and the workspace it then needs. */
+int lf_decode_auto_splits(int32_t B, int32_t Hkv, int32_t G, int32_t Skv, int32_t D);
+size_t lf_decode_workspace_bytes(int32_t B, int32_t Hkv, int32_t G, int32_t D, int32_t splits);
+
+/* Merge split-KV partials: part_o fp32 [units, splits, D], part_ml fp32 [units, splits, 2]
+ * (running max in log2 domain, sum) -> out bf16 rows; out row u lives at
+ * out + (u / G / Hkv) * o_stride[0] + ((u / G) % Hkv) * o_stride[1] + (u % G) * o_stride[2]. */
+int lf_combine_f32(const float* part_o, const float* part_ml, void* out, int32_t B, int32_t Hkv,
+                   int32_t G, int32_t D, int32_t splits, const int64_t* o_stride, void* stream);
+
+/* Gather only: out[b, h, t, :] = pool[block_table[b, t / page_size], t % page_size, h, :]. */
+int lf_paged_gather_bf16(const void* pool, const int32_t* block_table, void* out, int32_t B,
+                         int32_t Hkv, int32_t Skv, int32_t D, int32_t page_size, int32_t n_pages,
+                         const int64_t* pool_stride, int64_t bt_stride, int32_t* status,
+                         void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LF_SM100_H_ */

@@ -1,0 +1,121 @@
+"""ctypes binding of liblf_sm100.so (declarations mirror include/lf_sm100.h).
+
+Loading fails loudly: there is no Python or CPU substitute for the kernels.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "liblf_sm100.so"
+
+LF_MAX_MODS = 8
+
+# Every symbol include/lf_sm100.h declares.
+EXPORTS = [
+    "lf_query", "lf_strerror", "lf_last_cuda_error", "lf_prefill_bf16", "lf_skip_range",
+    "lf_decode_bf16", "lf_decode_paged_bf16", "lf_decode_auto_splits",
+    "lf_decode_workspace_bytes", "lf_combine_f32", "lf_paged_gather_bf16",
+]
+
+
+class LfPrefillArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p),
+        ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("Sq", C.c_int32),
+        ("Skv", C.c_int32), ("D", C.c_int32),
+        ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3),
+        ("v_stride", C.c_int64 * 3), ("o_stride", C.c_int64 * 3),
+        ("scale", C.c_float), ("n_mod", C.c_int32),
+        ("mod_op", C.c_int32 * LF_MAX_MODS), ("mod_arg", C.c_float * LF_MAX_MODS),
+        ("mask_kind", C.c_int32), ("window", C.c_int32), ("causal_offset", C.c_int32),
+        ("status", C.c_void_p), ("dbg_ranges", C.c_void_p),
+    ]
+
+
+class LfDecodeArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p),
+        ("B", C.c_int32), ("Hkv", C.c_int32), ("G", C.c_int32), ("Skv", C.c_int32),
+        ("D", C.c_int32),
+        ("q_stride", C.c_int64 * 3), ("o_stride", C.c_int64 * 3),
+        ("k_stride", C.c_int64 * 3), ("v_stride", C.c_int64 * 3),
+        ("scale", C.c_float), ("n_mod", C.c_int32),
+        ("mod_op", C.c_int32 * LF_MAX_MODS), ("mod_arg", C.c_float * LF_MAX_MODS),
+        ("block_table", C.c_void_p), ("block_table_v", C.c_void_p), ("bt_stride", C.c_int64),
+        ("page_size", C.c_int32), ("n_pages", C.c_int32),
+        ("splits", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("status", C.c_void_p),
+    ]
+
+
+class LfDeviceInfo(C.Structure):
+    _fields_ = [
+        ("abi_version", C.c_int32), ("device", C.c_int32), ("cc_major", C.c_int32),
+        ("cc_minor", C.c_int32), ("sm_count", C.c_int32), ("max_smem_optin", C.c_int32),
+        ("total_mem", C.c_int64),
+    ]
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the kernel library (once). Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m loopfuse_b200.build` "
+            "(needs nvcc). There is no fallback implementation.")
+    lib = C.CDLL(str(LIB_PATH))
+    lib.lf_query.argtypes = [C.POINTER(LfDeviceInfo)]
+    lib.lf_query.restype = C.c_int
+    lib.lf_strerror.argtypes = [C.c_int]
+    lib.lf_strerror.restype = C.c_char_p
+    lib.lf_last_cuda_error.argtypes = []
+    lib.lf_last_cuda_error.restype = C.c_char_p
+    lib.lf_prefill_bf16.argtypes = [C.POINTER(LfPrefillArgs), C.c_void_p]
+    lib.lf_prefill_bf16.restype = C.c_int
+    lib.lf_skip_range.argtypes = [C.c_int32] * 8 + [C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
+    lib.lf_skip_range.restype = None
+    for name in ("lf_decode_bf16", "lf_decode_paged_bf16"):
+        fn = getattr(lib, name)
+        fn.argtypes = [C.POINTER(LfDecodeArgs), C.c_void_p]
+        fn.restype = C.c_int
+    lib.lf_decode_auto_splits.argtypes = [C.c_int32] * 5
+    lib.lf_decode_auto_splits.restype = C.c_int
+    lib.lf_decode_workspace_bytes.argtypes = [C.c_int32] * 5
+    lib.lf_decode_workspace_bytes.restype = C.c_size_t
+    lib.lf_combine_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+                                   C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int64),
+                                   C.c_void_p]
+    lib.lf_combine_f32.restype = C.c_int
+    lib.lf_paged_gather_bf16.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
+                                         C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                         C.POINTER(C.c_int64), C.c_int64, C.c_void_p,
+                                         C.c_void_p]
+    lib.lf_paged_gather_bf16.restype = C.c_int
+    _lib = lib
+    return lib
+
+
+class LfError(RuntimeError):
+    pass
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        lib = load()
+        msg = lib.lf_strerror(rc).decode()
+        cuda = lib.lf_last_cuda_error().decode()
+        raise LfError(f"{what} failed: {msg} [{rc}]" + (f" - {cuda}" if rc == -5 and cuda else ""))
+
+
+def c_skip_range(mask_kind: int, window: int, causal_offset: int, s_q: int, s_kv: int,
+                 tile_q: int, tile_k: int, iq: int) -> tuple[int, int]:
+    lo, hi = C.c_int32(), C.c_int32()
+    load().lf_skip_range(mask_kind, window, causal_offset, s_q, s_kv, tile_q, tile_k, iq,
+                         C.byref(lo), C.byref(hi))
+    return lo.value, hi.value

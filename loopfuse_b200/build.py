@@ -1,0 +1,86 @@
+"""Build liblf_sm100.so (the C-ABI kernel library) in-tree with nvcc for sm_100a.
+
+Usage: ``python -m loopfuse_b200.build [--force] [--verbose]``. The build needs only nvcc; it
+cross-compiles on hosts without a GPU. The library is written next to this file so that it
+travels with the source tree.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent
+CSRC = PKG_DIR / "csrc"
+LIB_PATH = PKG_DIR / "liblf_sm100.so"
+STAMP_PATH = PKG_DIR / "csrc" / ".build_stamp"
+
+SOURCES = ["lf_api.cu", "lf_decode.cu", "lf_prefill.cu"]
+HEADERS = ["lf_common.cuh", "lf_skip_range.h", "../../include/lf_sm100.h"]
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-O3", "-std=c++17", "-lineinfo",
+    "--use_fast_math",
+    "-Xcompiler", "-fPIC",
+    "-Xptxas", "-v",
+]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    raise RuntimeError("nvcc not found: cannot build liblf_sm100.so")
+
+
+def _existing_sources() -> list[str]:
+    return [s for s in SOURCES if (CSRC / s).exists()]
+
+
+def _fingerprint() -> str:
+    h = hashlib.sha256()
+    for name in _existing_sources() + HEADERS:
+        h.update(name.encode())
+        h.update((CSRC / name).read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def build_native(force: bool = False, verbose: bool = False) -> Path:
+    """Compile every .cu under csrc/ into liblf_sm100.so; skip when sources are unchanged."""
+    fp = _fingerprint()
+    if not force and LIB_PATH.exists() and STAMP_PATH.exists() and STAMP_PATH.read_text() == fp:
+        return LIB_PATH
+    nvcc = _nvcc()
+    objs = []
+    log = []
+    procs = []
+    for src in _existing_sources():
+        obj = CSRC / (src[:-3] + ".o")
+        cmd = [nvcc, *NVCC_FLAGS, "-c", str(CSRC / src), "-o", str(obj)]
+        procs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE,
+                                                 stderr=subprocess.STDOUT, text=True)))
+    for src, obj, proc in procs:
+        out, _ = proc.communicate()
+        log.append(f"== {src}\n{out}")
+        if proc.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {src}:\n{out}")
+        objs.append(str(obj))
+    cmd = [nvcc, "-shared", "-o", str(LIB_PATH), *objs, "-lcudart"]
+    out = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if out.returncode != 0:
+        raise RuntimeError(f"link failed:\n{out.stdout}")
+    (CSRC / "build.log").write_text("\n".join(log))
+    STAMP_PATH.write_text(fp)
+    if verbose:
+        print("\n".join(log))
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    path = build_native(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    print(path)

@@ -1,0 +1,581 @@
+// Decode attention for sm_100a: one query row per head, KV streamed once from HBM.
+//
+// Bandwidth-bound, so the work is laid out to keep many 16-byte loads in flight:
+//   * a CTA owns one (batch, kv head, KV split); its 4 warps interleave over the tokens of
+//     the split, each thread issuing UNROLL K-row and UNROLL V-row 16-byte streaming loads
+//     before any arithmetic;
+//   * a K/V row of D bf16 is covered by D/8 lanes, so a warp reads 32/(D/8) whole rows per
+//     load instruction (fully used 32-byte sectors);
+//   * the G query heads that share the kv head are kept in registers and reuse every loaded
+//     row (GQA), scores are reduced with shuffles, softmax is online in the log2 domain;
+//   * with splits > 1 each CTA writes an un-normalised partial (acc, max, sum) to the
+//     workspace and lf_combine merges them (log-sum-exp combine);
+//   * the paged variant stages its slice of the block table through shared memory, checks
+//     every page id against the pool size (status word, clamped, never a trap) and turns
+//     (page, slot) into row pointers.
+#include "lf_common.cuh"
+
+#include <math.h>
+
+namespace lf {
+
+constexpr int kDecodeWarps = 4;
+constexpr int kDecodeThreads = kDecodeWarps * 32;
+constexpr int kDecodeUnroll = 4;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct DecodeParams {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  __nv_bfloat16* out;
+  float* part_o;   // [units, splits, D]
+  float* part_ml;  // [units, splits, 2]
+  const int32_t* block_table;
+  const int32_t* block_table_v;  // never null for the paged kernel (may equal block_table)
+  int32_t* status;
+  int64_t q_stride[3], o_stride[3], k_stride[3], v_stride[3];
+  int64_t bt_stride;
+  int32_t B, Hkv, Skv, splits, chunk;  // chunk = tokens per split
+  int32_t page_size, page_shift, n_pages;  // page_shift >= 0 when page_size is 2^shift
+  float scale;
+  ModChain mods;
+};
+
+template <int D, int G, bool PAGED, bool HAS_MOD>
+__global__ void __launch_bounds__(kDecodeThreads)
+    decode_split_kernel(const DecodeParams p) {
+  constexpr int LPR = D / 8;        // lanes per K/V row
+  constexpr int RPW = 32 / LPR;     // rows per warp-wide load
+  constexpr int U = kDecodeUnroll;  // rows in flight per thread and tensor
+  constexpr int TOK_PER_WARP_IT = U * RPW;
+  constexpr int TOK_PER_CTA_IT = TOK_PER_WARP_IT * kDecodeWarps;
+
+  const int split = blockIdx.x;
+  const int kvh = blockIdx.y;
+  const int b = blockIdx.z;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int rg = lane / LPR;   // row group inside the warp
+  const int col = lane % LPR;  // which 8-element slice of the row
+
+  const int t0 = split * p.chunk;
+  const int t1 = min(p.Skv, t0 + p.chunk);
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  // Layout: [page ids of this split] (paged only), then the cross-warp merge area.
+  int32_t* s_pages_k = reinterpret_cast<int32_t*>(smem_raw);
+  int32_t* s_pages_v = s_pages_k;
+  int n_pages_local = 0;
+  int first_page = 0;
+  size_t merge_off = 0;
+  if constexpr (PAGED) {
+    auto page_of = [&](int t) { return p.page_shift >= 0 ? (t >> p.page_shift) : (t / p.page_size); };
+    if (t1 > t0) {
+      first_page = page_of(t0);
+      n_pages_local = page_of(t1 - 1) - first_page + 1;
+    }
+    const bool two_tables = p.block_table_v != p.block_table;
+    const int pages_pad = (n_pages_local + 3) & ~3;
+    if (two_tables) s_pages_v = s_pages_k + pages_pad;
+    merge_off = static_cast<size_t>(pages_pad) * 4 * (two_tables ? 2 : 1);
+    for (int which = 0; which < (two_tables ? 2 : 1); ++which) {
+      const int32_t* bt = (which == 0 ? p.block_table : p.block_table_v) +
+                          static_cast<int64_t>(b) * p.bt_stride + first_page;
+      int32_t* dst = which == 0 ? s_pages_k : s_pages_v;
+      for (int i = threadIdx.x; i < n_pages_local; i += kDecodeThreads) {
+        int32_t pg = bt[i];
+        if (pg < 0 || pg >= p.n_pages) {
+          if (p.status) atomicExch(p.status, LF_DEV_BAD_PAGE);
+          pg = 0;
+        }
+        dst[i] = pg;
+      }
+    }
+    __syncthreads();
+  }
+  float* s_merge = reinterpret_cast<float*>(smem_raw + merge_off);
+
+  // Query rows for the G grouped heads, this lane's 8-element slice, as fp32. Without a
+  // score-mod chain the softmax scale and log2(e) are folded into q.
+  float qf[G][8];
+  {
+    const float qmul = HAS_MOD ? p.scale : p.scale * kLog2e;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const __nv_bfloat16* qp =
+          p.q + b * p.q_stride[0] + kvh * p.q_stride[1] + g * p.q_stride[2] + col * 8;
+      const uint4 raw = *reinterpret_cast<const uint4*>(qp);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        qf[g][2 * i] = bf16lo_to_f32(w[i]) * qmul;
+        qf[g][2 * i + 1] = bf16hi_to_f32(w[i]) * qmul;
+      }
+    }
+  }
+
+  float m_run[G], l_run[G], acc[G][8];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m_run[g] = -INFINITY;
+    l_run[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+  }
+
+  const __nv_bfloat16* kbase;
+  const __nv_bfloat16* vbase;
+  if constexpr (PAGED) {
+    kbase = p.k + kvh * p.k_stride[2] + col * 8;
+    vbase = p.v + kvh * p.v_stride[2] + col * 8;
+  } else {
+    kbase = p.k + b * p.k_stride[0] + kvh * p.k_stride[1] + col * 8;
+    vbase = p.v + b * p.v_stride[0] + kvh * p.v_stride[1] + col * 8;
+  }
+
+  for (int base = t0 + warp * TOK_PER_WARP_IT; base < t1; base += TOK_PER_CTA_IT) {
+    uint4 kr[U], vr[U];
+    bool valid[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int t = base + u * RPW + rg;
+      valid[u] = t < t1;
+      const int tc = valid[u] ? t : (t1 - 1);  // clamp: the row is loaded but scored -inf
+      int64_t koff, voff;
+      if constexpr (PAGED) {
+        const int pg_abs = p.page_shift >= 0 ? (tc >> p.page_shift) : (tc / p.page_size);
+        const int slot = tc - pg_abs * p.page_size;
+        const int64_t pgk = s_pages_k[pg_abs - first_page];
+        const int64_t pgv = s_pages_v[pg_abs - first_page];
+        koff = pgk * p.k_stride[0] + slot * p.k_stride[1];
+        voff = pgv * p.v_stride[0] + slot * p.v_stride[1];
+      } else {
+        koff = tc * p.k_stride[2];
+        voff = tc * p.v_stride[2];
+      }
+      kr[u] = ldg_stream_16(kbase + koff);
+      vr[u] = ldg_stream_16(vbase + voff);
+    }
+
+    // Scores: partial dot over this lane's 8 elements, then all-reduce over the row's lanes.
+    float s[G][U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t w[4] = {kr[u].x, kr[u].y, kr[u].z, kr[u].w};
+      float kf[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        kf[2 * i] = bf16lo_to_f32(w[i]);
+        kf[2 * i + 1] = bf16hi_to_f32(w[i]);
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float d = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) d = fmaf(qf[g][e], kf[e], d);
+        s[g][u] = d;
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        float d = s[g][u];
+#pragma unroll
+        for (int off = LPR / 2; off >= 1; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+        if constexpr (HAS_MOD) d = apply_mods(p.mods, d) * kLog2e;
+        s[g][u] = valid[u] ? d : -INFINITY;
+      }
+    }
+
+    // Online softmax update (log2 domain) and PV accumulation.
+    float pw[G][U];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float m_new = m_run[g];
+#pragma unroll
+      for (int u = 0; u < U; ++u) m_new = fmaxf(m_new, s[g][u]);
+      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = ex2_approx(m_run[g] - m_safe);
+      float psum = 0.f;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        pw[g][u] = ex2_approx(s[g][u] - m_safe);
+        psum += pw[g][u];
+      }
+      l_run[g] = l_run[g] * alpha + psum;
+      m_run[g] = m_new;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[g][e] *= alpha;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t w[4] = {vr[u].x, vr[u].y, vr[u].z, vr[u].w};
+      float vf[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        vf[2 * i] = bf16lo_to_f32(w[i]);
+        vf[2 * i + 1] = bf16hi_to_f32(w[i]);
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pw[g][u], vf[e], acc[g][e]);
+      }
+    }
+  }
+
+  // Merge the row groups of a warp (they hold disjoint token subsets of the same columns).
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+#pragma unroll
+    for (int off = LPR; off < 32; off <<= 1) {
+      const float m_o = __shfl_xor_sync(0xffffffffu, m_run[g], off);
+      const float l_o = __shfl_xor_sync(0xffffffffu, l_run[g], off);
+      const float m_new = fmaxf(m_run[g], m_o);
+      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+      const float a_s = ex2_approx(m_run[g] - m_safe);
+      const float a_o = ex2_approx(m_o - m_safe);
+      l_run[g] = l_run[g] * a_s + l_o * a_o;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float acc_o = __shfl_xor_sync(0xffffffffu, acc[g][e], off);
+        acc[g][e] = acc[g][e] * a_s + acc_o * a_o;
+      }
+      m_run[g] = m_new;
+    }
+  }
+
+  // Merge the warps through shared memory: s_merge[warp][g][0..D) acc, then m, l.
+  constexpr int kStride = D + 2;
+  if (rg == 0) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float* dst = s_merge + (warp * G + g) * kStride;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dst[col * 8 + e] = acc[g][e];
+      if (col == 0) {
+        dst[D] = m_run[g];
+        dst[D + 1] = l_run[g];
+      }
+    }
+  }
+  __syncthreads();
+
+  // One thread per (g, column) finishes the merge and writes the result.
+  for (int idx = threadIdx.x; idx < G * D; idx += kDecodeThreads) {
+    const int g = idx / D;
+    const int c = idx - g * D;
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w)
+      m_all = fmaxf(m_all, s_merge[(w * G + g) * kStride + D]);
+    const float m_safe = (m_all == -INFINITY) ? 0.f : m_all;
+    float l_all = 0.f, o = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w) {
+      const float* src = s_merge + (w * G + g) * kStride;
+      const float a = ex2_approx(src[D] - m_safe);
+      l_all += src[D + 1] * a;
+      o += src[c] * a;
+    }
+    const int64_t unit = (static_cast<int64_t>(b) * p.Hkv + kvh) * G + g;
+    if (p.splits == 1) {
+      __nv_bfloat16* op = p.out + b * p.o_stride[0] + kvh * p.o_stride[1] + g * p.o_stride[2];
+      op[c] = __float2bfloat16_rn(o / l_all);
+    } else {
+      p.part_o[(unit * p.splits + split) * D + c] = o;
+      if (c == 0) {
+        p.part_ml[(unit * p.splits + split) * 2] = m_all;
+        p.part_ml[(unit * p.splits + split) * 2 + 1] = l_all;
+      }
+    }
+  }
+}
+
+// Log-sum-exp combine of split-KV partials: one warp per (batch, kv head, g) output row.
+template <int D>
+__global__ void __launch_bounds__(128)
+    combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                   __nv_bfloat16* __restrict__ out, int64_t units, int32_t Hkv, int32_t G,
+                   int32_t splits, int64_t os0, int64_t os1, int64_t os2) {
+  constexpr int EPL = D / 32;  // elements per lane
+  const int64_t unit = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (unit >= units) return;
+  const float* ml = part_ml + unit * splits * 2;
+  float m_all = -INFINITY;
+  for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, ml[2 * s]);
+  const float m_safe = (m_all == -INFINITY) ? 0.f : m_all;
+  float l_all = 0.f;
+  float o[EPL];
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) o[e] = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float a = ex2_approx(ml[2 * s] - m_safe);
+    l_all += ml[2 * s + 1] * a;
+    const float* src = part_o + (unit * splits + s) * D + lane * EPL;
+    if constexpr (EPL == 4) {
+      const float4 x = *reinterpret_cast<const float4*>(src);
+      o[0] += x.x * a; o[1] += x.y * a; o[2] += x.z * a; o[3] += x.w * a;
+    } else {
+      const float2 x = *reinterpret_cast<const float2*>(src);
+      o[0] += x.x * a; o[1] += x.y * a;
+    }
+  }
+  const float inv = 1.f / l_all;
+  const int64_t g = unit % G;
+  const int64_t h = (unit / G) % Hkv;
+  const int64_t bb = unit / G / Hkv;
+  __nv_bfloat16* op = out + bb * os0 + h * os1 + g * os2 + lane * EPL;
+  if constexpr (EPL == 4) {
+    uint2 w;
+    w.x = pack_bf16x2(o[0] * inv, o[1] * inv);
+    w.y = pack_bf16x2(o[2] * inv, o[3] * inv);
+    *reinterpret_cast<uint2*>(op) = w;
+  } else {
+    *reinterpret_cast<uint32_t*>(op) = pack_bf16x2(o[0] * inv, o[1] * inv);
+  }
+}
+
+// out[b, h, t, :] = pool[block_table[b, t / P], t % P, h, :]; one warp-row group per token.
+template <int D>
+__global__ void __launch_bounds__(256)
+    paged_gather_kernel(const __nv_bfloat16* __restrict__ pool,
+                        const int32_t* __restrict__ block_table, __nv_bfloat16* __restrict__ out,
+                        int32_t B, int32_t Hkv, int32_t Skv, int32_t page_size, int32_t n_pages,
+                        int64_t ps0, int64_t ps1, int64_t ps2, int64_t bt_stride,
+                        int32_t* status) {
+  constexpr int LPR = D / 8;
+  const int64_t gid = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  const int64_t row = gid / LPR;
+  const int col = static_cast<int>(gid % LPR);
+  const int64_t total_rows = static_cast<int64_t>(B) * Hkv * Skv;
+  if (row >= total_rows) return;
+  const int t = static_cast<int>(row % Skv);
+  const int h = static_cast<int>((row / Skv) % Hkv);
+  const int b = static_cast<int>(row / Skv / Hkv);
+  int32_t pg = block_table[b * bt_stride + t / page_size];
+  if (pg < 0 || pg >= n_pages) {
+    if (status) atomicExch(status, LF_DEV_BAD_PAGE);
+    pg = 0;
+  }
+  const int slot = t % page_size;
+  const uint4 x = *reinterpret_cast<const uint4*>(pool + pg * ps0 + slot * ps1 + h * ps2 + col * 8);
+  *reinterpret_cast<uint4*>(out + row * D + col * 8) = x;
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------
+static int device_sm_count() {
+  static thread_local int cached_dev = -1, cached = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev != cached_dev) {
+    cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
+    cached_dev = dev;
+  }
+  return cached > 0 ? cached : 148;
+}
+
+static int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+static int choose_splits(int B, int Hkv, int G, int Skv, int D) {
+  (void)G;
+  (void)D;
+  const int units = B * Hkv;
+  const int sms = device_sm_count();
+  // Aim for >= 6 waves of 8 resident CTAs per SM so the tail wave is cheap, but keep at
+  // least 256 tokens per split so the per-CTA prologue/epilogue stays amortised.
+  const int want = (sms * 8 * 6 + units - 1) / units;
+  int max_by_len = Skv / 256;
+  if (max_by_len < 1) max_by_len = 1;
+  int s = want < max_by_len ? want : max_by_len;
+  if (s < 1) s = 1;
+  if (s > 32) s = 32;
+  return s;
+}
+
+template <int D, int G, bool PAGED>
+static int launch_decode_g(const DecodeParams& p, cudaStream_t st, size_t smem) {
+  dim3 grid(p.splits, p.Hkv, p.B);
+  if (p.mods.n > 0)
+    decode_split_kernel<D, G, PAGED, true><<<grid, kDecodeThreads, smem, st>>>(p);
+  else
+    decode_split_kernel<D, G, PAGED, false><<<grid, kDecodeThreads, smem, st>>>(p);
+  return check_launch("decode_split_kernel");
+}
+
+template <int D, bool PAGED>
+static int launch_decode(const DecodeParams& p, int G, cudaStream_t st, size_t smem) {
+  switch (G) {
+    case 1: return launch_decode_g<D, 1, PAGED>(p, st, smem);
+    case 2: return launch_decode_g<D, 2, PAGED>(p, st, smem);
+    case 4: return launch_decode_g<D, 4, PAGED>(p, st, smem);
+    case 8: return launch_decode_g<D, 8, PAGED>(p, st, smem);
+    default: return LF_ERR_UNSUPPORTED;
+  }
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int decode_impl(const LfDecodeArgs* a, void* stream, bool paged) {
+  if (!a || !a->q || !a->k || !a->v || !a->out) return LF_ERR_INVALID_ARG;
+  if (a->B <= 0 || a->Hkv <= 0 || a->G <= 0 || a->Skv <= 0) return LF_ERR_INVALID_ARG;
+  if (a->D != 64 && a->D != 128) return LF_ERR_UNSUPPORTED;
+  if (a->G != 1 && a->G != 2 && a->G != 4 && a->G != 8) return LF_ERR_UNSUPPORTED;
+  if (a->n_mod < 0 || a->n_mod > LF_MAX_MODS) return LF_ERR_INVALID_ARG;
+  if (a->Hkv > 65535 || a->B > 65535) return LF_ERR_TOO_LARGE;
+  if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->out))
+    return LF_ERR_ALIGNMENT;
+  for (int i = 0; i < 3; ++i) {
+    if ((a->q_stride[i] % 8) || (a->k_stride[i] % 8) || (a->v_stride[i] % 8) ||
+        (a->o_stride[i] % 4))
+      return LF_ERR_ALIGNMENT;
+  }
+  if (paged) {
+    if (!a->block_table || a->page_size <= 0 || a->n_pages <= 0) return LF_ERR_INVALID_ARG;
+  }
+  int splits = a->splits;
+  if (splits < 0) return LF_ERR_INVALID_ARG;
+  if (splits == 0) splits = choose_splits(a->B, a->Hkv, a->G, a->Skv, a->D);
+  // Token chunk per split: a multiple of 64 (and of the page size when that is a power of
+  // two up to 64), so a split never starts in the middle of a warp's token batch.
+  int chunk = round_up((a->Skv + splits - 1) / splits, 64);
+  splits = (a->Skv + chunk - 1) / chunk;
+  if (splits > 1) {
+    const size_t need = lf_decode_workspace_bytes(a->B, a->Hkv, a->G, a->D, splits);
+    if (!a->workspace || a->workspace_bytes < need) return LF_ERR_WORKSPACE;
+    if (!aligned16(a->workspace)) return LF_ERR_ALIGNMENT;
+  }
+
+  DecodeParams p;
+  p.q = static_cast<const __nv_bfloat16*>(a->q);
+  p.k = static_cast<const __nv_bfloat16*>(a->k);
+  p.v = static_cast<const __nv_bfloat16*>(a->v);
+  p.out = static_cast<__nv_bfloat16*>(a->out);
+  const int64_t units = static_cast<int64_t>(a->B) * a->Hkv * a->G;
+  p.part_o = static_cast<float*>(a->workspace);
+  p.part_ml = p.part_o ? p.part_o + units * splits * a->D : nullptr;
+  p.block_table = a->block_table;
+  p.block_table_v = a->block_table_v ? a->block_table_v : a->block_table;
+  p.status = a->status;
+  for (int i = 0; i < 3; ++i) {
+    p.q_stride[i] = a->q_stride[i];
+    p.o_stride[i] = a->o_stride[i];
+    p.k_stride[i] = a->k_stride[i];
+    p.v_stride[i] = a->v_stride[i];
+  }
+  p.bt_stride = a->bt_stride;
+  p.B = a->B;
+  p.Hkv = a->Hkv;
+  p.Skv = a->Skv;
+  p.splits = splits;
+  p.chunk = chunk;
+  p.page_size = paged ? a->page_size : 1;
+  p.page_shift = -1;
+  for (int sh = 0; sh < 31; ++sh)
+    if ((1 << sh) == p.page_size) p.page_shift = sh;
+  p.n_pages = paged ? a->n_pages : 0;
+  p.scale = a->scale;
+  p.mods.n = a->n_mod;
+  for (int i = 0; i < LF_MAX_MODS; ++i) {
+    p.mods.op[i] = i < a->n_mod ? a->mod_op[i] : 0;
+    p.mods.arg[i] = i < a->n_mod ? a->mod_arg[i] : 0.f;
+  }
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  size_t smem = static_cast<size_t>(kDecodeWarps) * a->G * (a->D + 2) * sizeof(float);
+  if (paged) smem += 2 * (((static_cast<size_t>(chunk / p.page_size) + 2 + 3) & ~size_t(3)) * 4);
+  if (smem > 48 * 1024) return LF_ERR_TOO_LARGE;
+
+  int rc;
+  if (a->D == 128)
+    rc = paged ? launch_decode<128, true>(p, a->G, st, smem)
+               : launch_decode<128, false>(p, a->G, st, smem);
+  else
+    rc = paged ? launch_decode<64, true>(p, a->G, st, smem)
+               : launch_decode<64, false>(p, a->G, st, smem);
+  if (rc != LF_OK) return rc;
+  if (splits > 1)
+    rc = lf_combine_f32(p.part_o, p.part_ml, a->out, a->B, a->Hkv, a->G, a->D, splits,
+                        a->o_stride, stream);
+  return rc;
+}
+
+}  // namespace lf
+
+extern "C" {
+
+int lf_decode_auto_splits(int32_t B, int32_t Hkv, int32_t G, int32_t Skv, int32_t D) {
+  if (B <= 0 || Hkv <= 0 || Skv <= 0) return 1;
+  int splits = lf::choose_splits(B, Hkv, G, Skv, D);
+  const int chunk = lf::round_up((Skv + splits - 1) / splits, 64);
+  return (Skv + chunk - 1) / chunk;
+}
+
+size_t lf_decode_workspace_bytes(int32_t B, int32_t Hkv, int32_t G, int32_t D, int32_t splits) {
+  if (splits <= 1) return 0;
+  const size_t units = static_cast<size_t>(B) * Hkv * G;
+  return units * splits * (static_cast<size_t>(D) + 2) * sizeof(float);
+}
+
+int lf_decode_bf16(const LfDecodeArgs* args, void* stream) {
+  return lf::decode_impl(args, stream, false);
+}
+
+int lf_decode_paged_bf16(const LfDecodeArgs* args, void* stream) {
+  return lf::decode_impl(args, stream, true);
+}
+
+int lf_combine_f32(const float* part_o, const float* part_ml, void* out, int32_t B, int32_t Hkv,
+                   int32_t G, int32_t D, int32_t splits, const int64_t* o_stride, void* stream) {
+  if (!part_o || !part_ml || !out || !o_stride) return LF_ERR_INVALID_ARG;
+  if (B <= 0 || Hkv <= 0 || G <= 0 || splits <= 0) return LF_ERR_INVALID_ARG;
+  if (D != 64 && D != 128) return LF_ERR_UNSUPPORTED;
+  const int64_t units = static_cast<int64_t>(B) * Hkv * G;
+  const unsigned blocks = static_cast<unsigned>((units + 3) / 4);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (D == 128)
+    lf::combine_kernel<128><<<blocks, 128, 0, st>>>(part_o, part_ml,
+                                                    static_cast<__nv_bfloat16*>(out), units, Hkv,
+                                                    G, splits, o_stride[0], o_stride[1],
+                                                    o_stride[2]);
+  else
+    lf::combine_kernel<64><<<blocks, 128, 0, st>>>(part_o, part_ml,
+                                                   static_cast<__nv_bfloat16*>(out), units, Hkv,
+                                                   G, splits, o_stride[0], o_stride[1],
+                                                   o_stride[2]);
+  return lf::check_launch("combine_kernel");
+}
+
+int lf_paged_gather_bf16(const void* pool, const int32_t* block_table, void* out, int32_t B,
+                         int32_t Hkv, int32_t Skv, int32_t D, int32_t page_size, int32_t n_pages,
+                         const int64_t* pool_stride, int64_t bt_stride, int32_t* status,
+                         void* stream) {
+  if (!pool || !block_table || !out || !pool_stride) return LF_ERR_INVALID_ARG;
+  if (B <= 0 || Hkv <= 0 || Skv <= 0 || page_size <= 0 || n_pages <= 0)
+    return LF_ERR_INVALID_ARG;
+  if (D != 64 && D != 128) return LF_ERR_UNSUPPORTED;
+  if (!lf::aligned16(pool) || !lf::aligned16(out)) return LF_ERR_ALIGNMENT;
+  for (int i = 0; i < 3; ++i)
+    if (pool_stride[i] % 8) return LF_ERR_ALIGNMENT;
+  const int64_t threads = static_cast<int64_t>(B) * Hkv * Skv * (D / 8);
+  const unsigned blocks = static_cast<unsigned>((threads + 255) / 256);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (D == 128)
+    lf::paged_gather_kernel<128><<<blocks, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(pool), block_table, static_cast<__nv_bfloat16*>(out),
+        B, Hkv, Skv, page_size, n_pages, pool_stride[0], pool_stride[1], pool_stride[2],
+        bt_stride, status);
+  else
+    lf::paged_gather_kernel<64><<<blocks, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(pool), block_table, static_cast<__nv_bfloat16*>(out),
+        B, Hkv, Skv, page_size, n_pages, pool_stride[0], pool_stride[1], pool_stride[2],
+        bt_stride, status);
+  return lf::check_launch("paged_gather_kernel");
+}
+
+}  // extern "C"

@@ -1,0 +1,627 @@
+// Prefill attention for sm_100a: TMA-staged tiles, tcgen05 MMA with accumulators in tensor
+// memory, online softmax in registers.
+//
+// One CTA owns two consecutive 128-row query tiles of one (batch, q head) and walks the KV
+// tiles that the skip range leaves (fully masked tiles are never loaded or multiplied).
+//
+//   warps 0-3   softmax for query tile 0 (one thread per score row)
+//   warps 4-7   softmax for query tile 1
+//   warp  8     TMA producer: Q tiles once, then K(j), V(j), K(j+1), ... into a ring
+//   warp  9     MMA issuer (one thread): S_t = Q_t K^T, O_t += P_t V
+//
+// Tensor memory (512 columns x 128 lanes of 32 bit):
+//   [0,128)    S_0 (fp32); P_0 (bf16, two per column) overwrites columns [0,64)
+//   [128,256)  S_1 / P_1
+//   [256,256+D) O_0     [384,384+D) O_1
+//
+// The two query tiles ping-pong on the tensor pipe: while the softmax warps of one tile turn
+// S into P, the MMA thread runs the other tile's PV and next QK^T. MMAs complete in issue
+// order, so "S_t(k) is ready" also means "O_t holds every PV up to k-1"; the softmax warps
+// use that to rescale O_t in place (only when the running max moved by more than 2^8).
+//
+// Shared-memory tiles use the 128-byte swizzle that TMA writes and the MMA descriptors read:
+// a [128 rows][D] bf16 tile is stored as D/64 blocks of [128][64] (128-byte rows).
+// No cluster launch and no multicast: every CTA fetches its own tiles; L2 provides the reuse
+// between the CTAs of one kv head.
+#include "lf_common.cuh"
+#include "lf_skip_range.h"
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <math.h>
+
+#include <mutex>
+
+namespace lf {
+
+constexpr int kTileQ = LF_PREFILL_TILE_Q;
+constexpr int kTileK = LF_PREFILL_TILE_K;
+constexpr int kPrefillThreads = 320;
+constexpr int kMaxStages = 8;
+// K/V ring depth: 4 x 32 KB tiles at D=128, 8 x 16 KB at D=64 (which also keeps the CTA above
+// half of the shared memory, so two CTAs never compete for the 512 tensor-memory columns).
+template <int D>
+struct StagesFor {
+  static constexpr int value = D == 64 ? 8 : 4;
+};
+constexpr float kLog2eF = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.0f;  // log2 domain
+
+constexpr int kModeNone = 0;     // logit2 = raw * c2
+constexpr int kModeSoftcap = 1;  // logit2 = tanh(raw * a) * c2
+constexpr int kModeGeneric = 2;  // logit2 = mods(raw * a) * c2
+
+struct PrefillParams {
+  __nv_bfloat16* out;
+  int64_t o_stride[3];
+  int32_t Sq, Skv, Hq, group;
+  int32_t mask_kind, window, causal_offset;
+  int32_t n_qtiles;  // ceil(Sq / 128)
+  float a;           // multiplies the raw dot product before the score function
+  float c2;          // multiplies the score-function output; includes log2(e); > 0
+  ModChain mods;
+  int32_t* status;
+  int32_t* dbg_ranges;
+};
+
+// Barrier block at the start of shared memory.
+struct __align__(8) PrefillBarriers {
+  uint64_t q_full[2];
+  uint64_t kv_full[kMaxStages];
+  uint64_t kv_empty[kMaxStages];
+  uint64_t s_full[2];
+  uint64_t p_full[2];
+  uint64_t o_final[2];
+  uint32_t tmem_base;
+  uint32_t pad;
+};
+
+__device__ __forceinline__ void report_timeout(int32_t* status, int where) {
+  if (status) atomicCAS(status, LF_DEV_OK, LF_DEV_TIMEOUT | (where << 8));
+}
+
+template <int D, int MODE>
+__global__ void __launch_bounds__(kPrefillThreads, 1)
+    prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                   const __grid_constant__ CUtensorMap tmap_k,
+                   const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
+  constexpr int kStages = StagesFor<D>::value;
+  constexpr int kBlocksD = D / 64;                  // 64-column swizzle blocks per tile row
+  constexpr uint32_t kBlockBytes = kTileQ * 128;    // one [128][64] bf16 block
+  constexpr uint32_t kTileBytes = kBlockBytes * kBlocksD;
+  constexpr uint32_t kIdescQK = make_idesc_bf16(128, kTileK, 0);
+  constexpr uint32_t kIdescPV = make_idesc_bf16(128, D, 1);
+  constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
+
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~static_cast<uintptr_t>(1023));
+  PrefillBarriers* bars = reinterpret_cast<PrefillBarriers*>(smem);
+  unsigned char* sQ = smem + 1024;
+  unsigned char* sKV = sQ + 2 * kTileBytes;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // Heaviest query tiles first (causal work grows with the row index).
+  const int pair = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int hkv = h / p.group;
+  const int iq0 = pair * 2;
+
+  int lo_t[2], hi_t[2];
+  skip_range(p.mask_kind, p.window, p.causal_offset, p.Sq, p.Skv, kTileQ, kTileK, iq0, &lo_t[0],
+             &hi_t[0]);
+  skip_range(p.mask_kind, p.window, p.causal_offset, p.Sq, p.Skv, kTileQ, kTileK, iq0 + 1,
+             &lo_t[1], &hi_t[1]);
+  const bool tile_valid[2] = {iq0 * kTileQ < p.Sq, (iq0 + 1) * kTileQ < p.Sq};
+  const bool has_work[2] = {tile_valid[0] && hi_t[0] > lo_t[0], tile_valid[1] && hi_t[1] > lo_t[1]};
+  int lo = 0, hi = 0;
+  if (has_work[0] && has_work[1]) {
+    lo = min(lo_t[0], lo_t[1]);
+    hi = max(hi_t[0], hi_t[1]);
+  } else if (has_work[0]) {
+    lo = lo_t[0];
+    hi = hi_t[0];
+  } else if (has_work[1]) {
+    lo = lo_t[1];
+    hi = hi_t[1];
+  }
+
+  // ---------------- setup ----------------
+  if (warp == 9 && lane == 0) {
+    mbar_init(&bars->q_full[0], 1);
+    mbar_init(&bars->q_full[1], 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars->kv_full[s], 1);
+      mbar_init(&bars->kv_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&bars->s_full[t], 1);
+      mbar_init(&bars->p_full[t], 128);
+      mbar_init(&bars->o_final[t], 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 8 && lane == 0) {
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 0) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 8) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      for (int t = 0; t < 2; ++t) {
+        if (!has_work[t]) continue;
+        mbar_arrive_expect_tx(&bars->q_full[t], kTileBytes);
+#pragma unroll
+        for (int kb = 0; kb < kBlocksD; ++kb)
+          tma_load_4d(sQ + t * kTileBytes + kb * kBlockBytes, &tmap_q, &bars->q_full[t], kb * 64,
+                      (iq0 + t) * kTileQ, h, b);
+      }
+      int n = 0;
+      bool ok = true;
+      for (int j = lo; j < hi && ok; ++j) {
+        for (int which = 0; which < 2 && ok; ++which, ++n) {
+          const int stage = n % kStages;
+          const uint32_t parity = ((n / kStages) & 1) ^ 1;
+          if (!mbar_wait(&bars->kv_empty[stage], parity)) {
+            report_timeout(p.status, 1);
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&bars->kv_full[stage], kTileBytes);
+          const CUtensorMap* tm = which == 0 ? &tmap_k : &tmap_v;
+#pragma unroll
+          for (int kb = 0; kb < kBlocksD; ++kb)
+            tma_load_4d(sKV + stage * kTileBytes + kb * kBlockBytes, tm, &bars->kv_full[stage],
+                        kb * 64, j * kTileK, hkv, b);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0 && hi > lo) {
+      bool ok = true;
+      for (int t = 0; t < 2 && ok; ++t) {
+        if (has_work[t] && !mbar_wait(&bars->q_full[t], 0)) {
+          report_timeout(p.status, 2);
+          ok = false;
+        }
+      }
+      const uint32_t sQ_addr = smem_u32(sQ);
+      const uint32_t sKV_addr = smem_u32(sKV);
+      const uint32_t col_s[2] = {kColS0, kColS1};
+      const uint32_t col_o[2] = {kColO0, kColO1};
+      int kcount[2] = {0, 0};  // KV tiles issued so far per query tile
+
+      auto active = [&](int t, int j) { return has_work[t] && j >= lo_t[t] && j < hi_t[t]; };
+      auto issue_qk = [&](int t, int stage) {
+        const uint32_t qa = sQ_addr + t * kTileBytes;
+        const uint32_t ka = sKV_addr + stage * kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks / 4) * kBlockBytes + (ks % 4) * 32;
+          mma_ss(tmem_base + col_s[t], make_smem_desc_sw128(qa + off, 16, 1024),
+                 make_smem_desc_sw128(ka + off, 16, 1024), kIdescQK, ks > 0 ? 1u : 0u);
+        }
+        tc_commit(&bars->s_full[t]);
+      };
+      auto issue_pv = [&](int t, int stage, bool accumulate) {
+        const uint32_t va = sKV_addr + stage * kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < kTileK / 16; ++ks) {
+          mma_ts(tmem_base + col_o[t], tmem_base + col_s[t] + ks * 8,
+                 make_smem_desc_sw128(va + ks * 2048, kBlockBytes, 1024), kIdescPV,
+                 (accumulate || ks > 0) ? 1u : 0u);
+        }
+      };
+
+      if (ok) {
+        // Prologue: first QK^T of each tile that starts at `lo`.
+        const int stage = 0;
+        if (!mbar_wait(&bars->kv_full[stage], 0)) {
+          report_timeout(p.status, 3);
+          ok = false;
+        } else {
+          tc_fence_after();
+          if (active(0, lo)) issue_qk(0, stage);
+          if (active(1, lo)) issue_qk(1, stage);
+          tc_commit(&bars->kv_empty[stage]);
+        }
+      }
+      for (int j = lo; j < hi && ok; ++j) {
+        const int nv = 2 * (j - lo) + 1;
+        const int sv = nv % kStages;
+        if (!mbar_wait(&bars->kv_full[sv], (nv / kStages) & 1)) {
+          report_timeout(p.status, 4);
+          break;
+        }
+        const bool nxt = j + 1 < hi;
+        const int nk = nv + 1;
+        const int sk = nk % kStages;
+        if (nxt && !mbar_wait(&bars->kv_full[sk], (nk / kStages) & 1)) {
+          report_timeout(p.status, 5);
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (active(t, j)) {
+            if (!mbar_wait(&bars->p_full[t], kcount[t] & 1)) {
+              report_timeout(p.status, 6 + t);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            issue_pv(t, sv, kcount[t] > 0);
+            ++kcount[t];
+            if (j == hi_t[t] - 1) tc_commit(&bars->o_final[t]);
+          }
+          if (t == 1) tc_commit(&bars->kv_empty[sv]);
+          if (nxt && active(t, j + 1)) issue_qk(t, sk);
+        }
+        if (ok && nxt) tc_commit(&bars->kv_empty[sk]);
+      }
+    }
+  } else {
+    // ---------------- softmax warps ----------------
+    const int t = warp >> 2;                 // query tile of this warp group
+    const int row = (warp & 3) * 32 + lane;  // row inside the tile == tensor-memory lane
+    const int grow = (iq0 + t) * kTileQ + row;
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_addr + (t == 0 ? kColS0 : kColS1);
+    const uint32_t o_addr = tmem_base + lane_addr + (t == 0 ? kColO0 : kColO1);
+
+    if (p.dbg_ranges && tile_valid[t] && row == 0) {
+      const int64_t idx = ((static_cast<int64_t>(b) * p.Hq + h) * p.n_qtiles + (iq0 + t)) * 2;
+      p.dbg_ranges[idx] = lo_t[t];
+      p.dbg_ranges[idx + 1] = hi_t[t];
+    }
+
+    if (has_work[t]) {
+      // Visible column interval of this row: [c_lo, c_hi].
+      int c_hi = p.Skv - 1;
+      int c_lo = 0;
+      if (p.mask_kind != LF_MASK_NONE) c_hi = min(c_hi, grow + p.causal_offset);
+      if (p.mask_kind == LF_MASK_CAUSAL_WINDOW)
+        c_lo = max(0, grow + p.causal_offset - (p.window - 1));
+
+      float m_used = -INFINITY;  // max the stored P and O are scaled by (log2 domain)
+      float l_run = 0.f;
+      bool ok = true;
+      const int nblk = hi_t[t] - lo_t[t];
+      for (int k = 0; k < nblk; ++k) {
+        const int c0 = (lo_t[t] + k) * kTileK;
+        if (!mbar_wait(&bars->s_full[t], k & 1)) {
+          report_timeout(p.status, 8 + t);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        uint32_t sr[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(s_addr + c * 32, sr[c]);
+        tmem_wait_ld();
+
+        // Score function (before the log2e-scaled multiplier c2).
+        if constexpr (MODE == kModeSoftcap) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              sr[c][i] = __float_as_uint(tanh_approx(__uint_as_float(sr[c][i]) * p.a));
+        } else if constexpr (MODE == kModeGeneric) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              sr[c][i] = __float_as_uint(apply_mods(p.mods, __uint_as_float(sr[c][i]) * p.a));
+        }
+        // Mask only on tiles that cross the row's visible interval.
+        const int rel_lo = c_lo - c0;
+        const int rel_hi = c_hi - c0;
+        if (rel_lo > 0 || rel_hi < kTileK - 1) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int cc = c * 32 + i;
+              if (cc < rel_lo || cc > rel_hi) sr[c][i] = 0xff800000u;  // -inf
+            }
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sr[c][i]));
+        const float m_new = fmaxf(m_used, mx * p.c2);
+
+        // Lazy rescale: move the reference max only when it grew by more than 2^8.
+        float alpha = 1.f;
+        bool need = false;
+        if (m_new > -INFINITY && (m_used == -INFINITY || m_new - m_used > kRescaleThreshold)) {
+          need = true;
+          alpha = ex2_approx(m_used - m_new);  // 0 when m_used is -inf
+          m_used = m_new;
+        }
+        if (k > 0 && __any_sync(0xffffffffu, need)) {
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t orr[32];
+            tmem_ld_32x32b_x32(o_addr + c * 32, orr);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+            tmem_st_32x32b_x32(o_addr + c * 32, orr);
+          }
+        }
+        const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+        float psum = 0.f;
+        uint32_t pk[2][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c][i]), p.c2, -m_safe));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c][i + 1]), p.c2, -m_safe));
+            psum += p0 + p1;
+            pk[c >> 1][(c & 1) * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
+          }
+        l_run = l_run * alpha + psum;
+        tmem_st_32x32b_x32(s_addr, pk[0]);
+        tmem_st_32x32b_x32(s_addr + 32, pk[1]);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&bars->p_full[t]);
+      }
+
+      // Epilogue: O_t / l -> bf16 -> global (one row per thread).
+      if (ok) {
+        if (!mbar_wait(&bars->o_final[t], 0)) {
+          report_timeout(p.status, 10 + t);
+          ok = false;
+        }
+      }
+      if (ok) {
+        tc_fence_after();
+        const float inv = 1.f / l_run;
+        __nv_bfloat16* orow = p.out + b * p.o_stride[0] + h * p.o_stride[1] +
+                              static_cast<int64_t>(grow) * p.o_stride[2];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t orr[32];
+          tmem_ld_32x32b_x32(o_addr + c * 32, orr);
+          tmem_wait_ld();
+          if (grow < p.Sq) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(orr[i]) * inv, __uint_as_float(orr[i + 1]) * inv);
+              w.y = pack_bf16x2(__uint_as_float(orr[i + 2]) * inv,
+                                __uint_as_float(orr[i + 3]) * inv);
+              w.z = pack_bf16x2(__uint_as_float(orr[i + 4]) * inv,
+                                __uint_as_float(orr[i + 5]) * inv);
+              w.w = pack_bf16x2(__uint_as_float(orr[i + 6]) * inv,
+                                __uint_as_float(orr[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
+            }
+          }
+        }
+      }
+    } else if (tile_valid[t] && grow < p.Sq) {
+      // No visible key at all for this tile: softmax of an all -inf row is NaN in the
+      // eager computation, so the rows are written as NaN.
+      __nv_bfloat16* orow = p.out + b * p.o_stride[0] + h * p.o_stride[1] +
+                            static_cast<int64_t>(grow) * p.o_stride[2];
+      const uint4 nan4 = {0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u};
+#pragma unroll
+      for (int c = 0; c < D; c += 8) *reinterpret_cast<uint4*>(orow + c) = nan4;
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &ptr, 12000,
+                                                     cudaEnableDefault, &qres);
+    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+    else
+      set_cuda_error(e, "cudaGetDriverEntryPointByVersion(cuTensorMapEncodeTiled)");
+  });
+  return fn;
+}
+
+// Tensor map over a bf16 [B, H, S, D] tensor (innermost stride 1), box = [1, 1, 128, 64],
+// 128-byte swizzle, out-of-range rows read as zero.
+static int make_tile_map(CUtensorMap* map, const void* base, int B, int H, int S, int D,
+                         const int64_t* stride /* b, h, s in elements */) {
+  auto fn = get_encode_fn();
+  if (!fn) return LF_ERR_CUDA;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S),
+                        static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(B)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(stride[2]) * 2,
+                           static_cast<cuuint64_t>(stride[1]) * 2,
+                           static_cast<cuuint64_t>(stride[0]) * 2};
+  // A dimension of extent 1 may carry any stride; keep it a valid multiple of 16 bytes.
+  for (int i = 0; i < 3; ++i)
+    if (strides[i] == 0 || (strides[i] & 15)) {
+      if (dims[i + 1] == 1)
+        strides[i] = 16 * ((static_cast<cuuint64_t>(D) * 2 + 15) / 16);
+      else
+        return LF_ERR_ALIGNMENT;
+    }
+  cuuint32_t box[4] = {64, 128, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+    return LF_ERR_CUDA;
+  }
+  return LF_OK;
+}
+
+template <int D, int MODE>
+static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                          const PrefillParams& p, int B, cudaStream_t st) {
+  constexpr size_t kTileBytes = static_cast<size_t>(kTileQ) * D * 2;
+  constexpr size_t smem = 1024 /*align slack*/ + 1024 /*barriers*/ + 2 * kTileBytes +
+                          StagesFor<D>::value * kTileBytes;
+  static thread_local int configured_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_dev != dev) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_kernel<D, MODE>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) {
+      set_cuda_error(e, "cudaFuncSetAttribute(prefill_kernel)");
+      return LF_ERR_CUDA;
+    }
+    configured_dev = dev;
+  }
+  const int pairs = (p.n_qtiles + 1) / 2;
+  dim3 grid(pairs, p.Hq, B);
+  prefill_kernel<D, MODE><<<grid, kPrefillThreads, smem, st>>>(mq, mk, mv, p);
+  return check_launch("prefill_kernel");
+}
+
+static int prefill_impl(const LfPrefillArgs* a, void* stream) {
+  if (!a || !a->q || !a->k || !a->v || !a->out) return LF_ERR_INVALID_ARG;
+  if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Sq <= 0 || a->Skv <= 0)
+    return LF_ERR_INVALID_ARG;
+  if (a->Hq % a->Hkv) return LF_ERR_INVALID_ARG;
+  if (a->D != 64 && a->D != 128) return LF_ERR_UNSUPPORTED;
+  if (a->n_mod < 0 || a->n_mod > LF_MAX_MODS) return LF_ERR_INVALID_ARG;
+  if (a->mask_kind < LF_MASK_NONE || a->mask_kind > LF_MASK_CAUSAL_WINDOW)
+    return LF_ERR_INVALID_ARG;
+  if (a->mask_kind == LF_MASK_CAUSAL_WINDOW && a->window <= 0) return LF_ERR_INVALID_ARG;
+  if (a->Hq > 65535 || a->B > 65535) return LF_ERR_TOO_LARGE;
+  const void* ptrs[4] = {a->q, a->k, a->v, a->out};
+  for (const void* ptr : ptrs)
+    if (reinterpret_cast<uintptr_t>(ptr) & 15u) return LF_ERR_ALIGNMENT;
+  for (int i = 0; i < 3; ++i)
+    if (a->o_stride[i] % 8) return LF_ERR_ALIGNMENT;
+
+  PrefillParams p;
+  p.out = static_cast<__nv_bfloat16*>(a->out);
+  for (int i = 0; i < 3; ++i) p.o_stride[i] = a->o_stride[i];
+  p.Sq = a->Sq;
+  p.Skv = a->Skv;
+  p.Hq = a->Hq;
+  p.group = a->Hq / a->Hkv;
+  p.mask_kind = a->mask_kind;
+  p.window = a->window;
+  p.causal_offset = a->causal_offset;
+  p.n_qtiles = (a->Sq + kTileQ - 1) / kTileQ;
+  p.status = a->status;
+  p.dbg_ranges = a->dbg_ranges;
+  p.mods.n = 0;
+  for (int i = 0; i < LF_MAX_MODS; ++i) {
+    p.mods.op[i] = 0;
+    p.mods.arg[i] = 0.f;
+  }
+
+  // Pick the score-function mode. Leading and trailing constant multipliers are folded into
+  // `a` (before) and `c2` (after); c2 must stay positive for the max-before-scale shortcut.
+  int mode = kModeGeneric;
+  {
+    int i = 0;
+    float pre = a->scale;
+    while (i < a->n_mod && (a->mod_op[i] == LF_MOD_MUL || a->mod_op[i] == LF_MOD_DIV)) {
+      pre = a->mod_op[i] == LF_MOD_MUL ? pre * a->mod_arg[i] : pre / a->mod_arg[i];
+      ++i;
+    }
+    if (i == a->n_mod) {
+      if (pre > 0.f) {
+        mode = kModeNone;
+        p.a = 1.f;
+        p.c2 = pre * kLog2eF;
+      }
+    } else if (a->mod_op[i] == LF_MOD_TANH) {
+      int j = i + 1;
+      float post = 1.f;
+      while (j < a->n_mod && (a->mod_op[j] == LF_MOD_MUL || a->mod_op[j] == LF_MOD_DIV)) {
+        post = a->mod_op[j] == LF_MOD_MUL ? post * a->mod_arg[j] : post / a->mod_arg[j];
+        ++j;
+      }
+      if (j == a->n_mod && post > 0.f) {
+        mode = kModeSoftcap;
+        p.a = pre;
+        p.c2 = post * kLog2eF;
+      }
+    }
+    if (mode == kModeGeneric) {
+      p.a = a->scale;
+      p.c2 = kLog2eF;
+      p.mods.n = a->n_mod;
+      for (int m = 0; m < a->n_mod; ++m) {
+        p.mods.op[m] = a->mod_op[m];
+        p.mods.arg[m] = a->mod_arg[m];
+      }
+    }
+  }
+
+  CUtensorMap mq, mk, mv;
+  int rc = make_tile_map(&mq, a->q, a->B, a->Hq, a->Sq, a->D, a->q_stride);
+  if (rc != LF_OK) return rc;
+  rc = make_tile_map(&mk, a->k, a->B, a->Hkv, a->Skv, a->D, a->k_stride);
+  if (rc != LF_OK) return rc;
+  rc = make_tile_map(&mv, a->v, a->B, a->Hkv, a->Skv, a->D, a->v_stride);
+  if (rc != LF_OK) return rc;
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a->D == 128) {
+    if (mode == kModeNone) return launch_prefill<128, kModeNone>(mq, mk, mv, p, a->B, st);
+    if (mode == kModeSoftcap) return launch_prefill<128, kModeSoftcap>(mq, mk, mv, p, a->B, st);
+    return launch_prefill<128, kModeGeneric>(mq, mk, mv, p, a->B, st);
+  }
+  if (mode == kModeNone) return launch_prefill<64, kModeNone>(mq, mk, mv, p, a->B, st);
+  if (mode == kModeSoftcap) return launch_prefill<64, kModeSoftcap>(mq, mk, mv, p, a->B, st);
+  return launch_prefill<64, kModeGeneric>(mq, mk, mv, p, a->B, st);
+}
+
+}  // namespace lf
+
+extern "C" {
+
+int lf_prefill_bf16(const LfPrefillArgs* args, void* stream) {
+  return lf::prefill_impl(args, stream);
+}
+
+void lf_skip_range(int32_t mask_kind, int32_t window, int32_t causal_offset, int32_t Sq,
+                   int32_t Skv, int32_t tile_q, int32_t tile_k, int32_t iq, int32_t* lo,
+                   int32_t* hi) {
+  lf::skip_range(mask_kind, window, causal_offset, Sq, Skv, tile_q, tile_k, iq, lo, hi);
+}
+
+}  // extern "C"

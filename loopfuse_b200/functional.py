@@ -1,0 +1,261 @@
+"""Tensor-level entry points: torch CUDA tensors in, kernels of liblf_sm100.so out.
+
+These are what the compiled callable produced by ``loopfuse_backend`` calls; they can also be
+used directly. PyTorch only supplies device memory and the current stream here - all arithmetic
+happens in the library. Nothing in this module computes attention on the CPU or with torch ops.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from . import _native
+from .spec import MASK_NONE, MAX_MODS, ScoreMod, TILE_Q
+
+_DEV_TIMEOUT = 1
+_DEV_BAD_PAGE = 2
+
+
+def _require_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = tensors[0].device
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError(
+                "loopfuse_b200 kernels need CUDA tensors on an sm_100 GPU; there is no CPU path")
+        if t.device != dev:
+            raise ValueError("all tensors must live on the same device")
+    return dev
+
+
+def _check_bf16_lastdim(t: torch.Tensor, name: str) -> None:
+    if t.dtype != torch.bfloat16:
+        raise TypeError(f"{name} must be bfloat16, got {t.dtype}")
+    if t.stride(-1) != 1:
+        raise ValueError(f"{name} must have a contiguous last dim")
+
+
+def _fill_mods(args, scale: float, mods: Sequence[ScoreMod]) -> None:
+    if len(mods) > MAX_MODS:
+        raise ValueError(f"at most {MAX_MODS} score-mod ops")
+    args.scale = float(scale)
+    args.n_mod = len(mods)
+    for i, m in enumerate(mods):
+        args.mod_op[i] = int(m.op)
+        args.mod_arg[i] = float(m.arg)
+
+
+def _stream_ptr(dev: torch.device) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def new_status(device) -> torch.Tensor:
+    """A zeroed device word the kernels report device-side problems into."""
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def check_status(status: torch.Tensor, what: str = "kernel") -> None:
+    """Synchronising read of a status word; raises if a kernel recorded a problem."""
+    code = int(status.item())
+    if code == 0:
+        return
+    if (code & 0xFF) == _DEV_TIMEOUT:
+        raise RuntimeError(f"{what}: a bounded device-side wait ran out (site {code >> 8})")
+    if (code & 0xFF) == _DEV_BAD_PAGE:
+        raise RuntimeError(f"{what}: block_table holds a page id outside the pool")
+    raise RuntimeError(f"{what}: device status {code}")
+
+
+def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float = 1.0,
+                      mods: Sequence[ScoreMod] = (), mask_kind: int = MASK_NONE,
+                      window: int = 0, causal_offset: int = 0,
+                      out: Optional[torch.Tensor] = None,
+                      status: Optional[torch.Tensor] = None,
+                      dbg_ranges: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """softmax(mask(mods(scale * q k^T))) v for q [B,Hq,Sq,D], k/v [B,Hkv,Skv,D] (bf16)."""
+    dev = _require_cuda(q, k, v)
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _check_bf16_lastdim(t, n)
+        if t.dim() != 4:
+            raise ValueError(f"{n} must be 4-D")
+    B, Hq, Sq, D = q.shape
+    Bk, Hkv, Skv, Dk = k.shape
+    if v.shape != k.shape or Bk != B or Dk != D:
+        raise ValueError(f"shape mismatch: q {tuple(q.shape)} k {tuple(k.shape)} v {tuple(v.shape)}")
+    if Hq % Hkv:
+        raise ValueError("Hq must be a multiple of Hkv")
+    if out is None:
+        out = torch.empty((B, Hq, Sq, D), dtype=torch.bfloat16, device=dev)
+    else:
+        _require_cuda(out)
+        _check_bf16_lastdim(out, "out")
+    a = _native.LfPrefillArgs()
+    a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    a.B, a.Hq, a.Hkv, a.Sq, a.Skv, a.D = B, Hq, Hkv, Sq, Skv, D
+    for i in range(3):
+        a.q_stride[i] = q.stride(i)
+        a.k_stride[i] = k.stride(i)
+        a.v_stride[i] = v.stride(i)
+        a.o_stride[i] = out.stride(i)
+    _fill_mods(a, scale, mods)
+    a.mask_kind, a.window, a.causal_offset = int(mask_kind), int(window), int(causal_offset)
+    a.status = status.data_ptr() if status is not None else None
+    if dbg_ranges is not None:
+        need = B * Hq * (-(-Sq // TILE_Q)) * 2
+        if dbg_ranges.dtype != torch.int32 or dbg_ranges.numel() < need or not dbg_ranges.is_cuda:
+            raise ValueError(f"dbg_ranges must be a CUDA int32 tensor with >= {need} elements")
+        a.dbg_ranges = dbg_ranges.data_ptr()
+    with torch.cuda.device(dev):
+        rc = _native.load().lf_prefill_bf16(C.byref(a), _stream_ptr(dev))
+    _native.check(rc, "lf_prefill_bf16")
+    return out
+
+
+class DecodeWorkspace:
+    """Caller-owned scratch for split-KV partials, grown on demand and reused across calls."""
+
+    def __init__(self) -> None:
+        self._buf: Optional[torch.Tensor] = None
+
+    def get(self, nbytes: int, device) -> Optional[torch.Tensor]:
+        if nbytes == 0:
+            return None
+        if self._buf is None or self._buf.numel() < nbytes or self._buf.device != device:
+            self._buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        return self._buf
+
+
+_default_ws = DecodeWorkspace()
+
+
+def _decode_common(q, out, B, Hkv, G, Skv, D, scale, mods, splits, workspace, status, dev):
+    a = _native.LfDecodeArgs()
+    a.q, a.out = q.data_ptr(), out.data_ptr()
+    a.B, a.Hkv, a.G, a.Skv, a.D = B, Hkv, G, Skv, D
+    for i in range(3):
+        a.q_stride[i] = q.stride(i)
+        a.o_stride[i] = out.stride(i)
+    _fill_mods(a, scale, mods)
+    lib = _native.load()
+    with torch.cuda.device(dev):
+        n_splits = splits if splits else lib.lf_decode_auto_splits(B, Hkv, G, Skv, D)
+    a.splits = n_splits
+    nbytes = lib.lf_decode_workspace_bytes(B, Hkv, G, D, n_splits)
+    ws = (workspace or _default_ws).get(nbytes, dev)
+    a.workspace = ws.data_ptr() if ws is not None else None
+    a.workspace_bytes = nbytes
+    a.status = status.data_ptr() if status is not None else None
+    return a, ws
+
+
+def decode_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float = 1.0,
+                     mods: Sequence[ScoreMod] = (), splits: int = 0,
+                     out: Optional[torch.Tensor] = None,
+                     workspace: Optional[DecodeWorkspace] = None,
+                     status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Unmasked attention of G query rows per kv head: q [B,Hkv,G,D], k/v [B,Hkv,Skv,D]."""
+    dev = _require_cuda(q, k, v)
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _check_bf16_lastdim(t, n)
+        if t.dim() != 4:
+            raise ValueError(f"{n} must be 4-D")
+    B, Hkv, G, D = q.shape
+    if k.shape[0] != B or k.shape[1] != Hkv or k.shape[3] != D or v.shape != k.shape:
+        raise ValueError(f"shape mismatch: q {tuple(q.shape)} k {tuple(k.shape)} v {tuple(v.shape)}")
+    Skv = k.shape[2]
+    if out is None:
+        out = torch.empty((B, Hkv, G, D), dtype=torch.bfloat16, device=dev)
+    a, ws = _decode_common(q, out, B, Hkv, G, Skv, D, scale, mods, splits, workspace, status, dev)
+    a.k, a.v = k.data_ptr(), v.data_ptr()
+    for i in range(3):
+        a.k_stride[i] = k.stride(i)
+        a.v_stride[i] = v.stride(i)
+    with torch.cuda.device(dev):
+        rc = _native.load().lf_decode_bf16(C.byref(a), _stream_ptr(dev))
+    _native.check(rc, "lf_decode_bf16")
+    return out
+
+
+def _pool_view(pool: torch.Tensor, name: str) -> torch.Tensor:
+    _check_bf16_lastdim(pool, name)
+    if pool.dim() == 3:  # [pages, Hkv, D]: one token per page
+        pool = pool.unsqueeze(1)
+    if pool.dim() != 4:
+        raise ValueError(f"{name} must be [pages, page_size, Hkv, D] or [pages, Hkv, D]")
+    return pool
+
+
+def _table_i32(t: torch.Tensor) -> torch.Tensor:
+    if t.dim() != 2:
+        raise ValueError("block_table must be [batch, blocks]")
+    if t.dtype != torch.int32:
+        t = t.to(torch.int32)
+    if t.stride(1) != 1:
+        t = t.contiguous()
+    return t
+
+
+def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                           block_table: torch.Tensor, *, seq_len: Optional[int] = None,
+                           block_table_v: Optional[torch.Tensor] = None, scale: float = 1.0,
+                           mods: Sequence[ScoreMod] = (), splits: int = 0,
+                           out: Optional[torch.Tensor] = None,
+                           workspace: Optional[DecodeWorkspace] = None,
+                           status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decode attention over a paged KV cache: q [B,Hkv,G,D]; pools [pages, page_size, Hkv, D]
+    (or [pages, Hkv, D] for one-token pages); block_table int32 [B, blocks]. Token t of sequence
+    b lives at pool[block_table[b, t // page_size], t % page_size]."""
+    dev = _require_cuda(q, k_pool, v_pool, block_table)
+    _check_bf16_lastdim(q, "q")
+    k_pool = _pool_view(k_pool, "k_pool")
+    v_pool = _pool_view(v_pool, "v_pool")
+    B, Hkv, G, D = q.shape
+    n_pages, page_size = k_pool.shape[0], k_pool.shape[1]
+    if k_pool.shape[2] != Hkv or k_pool.shape[3] != D or v_pool.shape != k_pool.shape:
+        raise ValueError(f"pool shape mismatch: q {tuple(q.shape)} pool {tuple(k_pool.shape)}")
+    bt = _table_i32(block_table)
+    btv = _table_i32(block_table_v) if block_table_v is not None else None
+    if bt.shape[0] != B:
+        raise ValueError("block_table batch mismatch")
+    Skv = seq_len if seq_len is not None else bt.shape[1] * page_size
+    if Skv > bt.shape[1] * page_size:
+        raise ValueError("seq_len exceeds the block table")
+    if btv is not None and (btv.shape != bt.shape or btv.stride(0) != bt.stride(0)):
+        btv = btv.contiguous()
+        bt = bt.contiguous()
+    if out is None:
+        out = torch.empty((B, Hkv, G, D), dtype=torch.bfloat16, device=dev)
+    a, ws = _decode_common(q, out, B, Hkv, G, Skv, D, scale, mods, splits, workspace, status, dev)
+    a.k, a.v = k_pool.data_ptr(), v_pool.data_ptr()
+    for i in range(3):
+        a.k_stride[i] = k_pool.stride(i)
+        a.v_stride[i] = v_pool.stride(i)
+    a.block_table = bt.data_ptr()
+    a.block_table_v = btv.data_ptr() if btv is not None else None
+    a.bt_stride = bt.stride(0)
+    a.page_size, a.n_pages = page_size, n_pages
+    with torch.cuda.device(dev):
+        rc = _native.load().lf_decode_paged_bf16(C.byref(a), _stream_ptr(dev))
+    _native.check(rc, "lf_decode_paged_bf16")
+    return out
+
+
+def paged_gather(pool: torch.Tensor, block_table: torch.Tensor, *, seq_len: Optional[int] = None,
+                 status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Materialise [B, Hkv, S, D] from a paged pool (page-index check and paged prefill input)."""
+    dev = _require_cuda(pool, block_table)
+    pool = _pool_view(pool, "pool")
+    bt = _table_i32(block_table)
+    n_pages, page_size, Hkv, D = pool.shape
+    B = bt.shape[0]
+    S = seq_len if seq_len is not None else bt.shape[1] * page_size
+    out = torch.empty((B, Hkv, S, D), dtype=torch.bfloat16, device=dev)
+    strides = (C.c_int64 * 3)(pool.stride(0), pool.stride(1), pool.stride(2))
+    with torch.cuda.device(dev):
+        rc = _native.load().lf_paged_gather_bf16(
+            pool.data_ptr(), bt.data_ptr(), out.data_ptr(), B, Hkv, S, D, page_size, n_pages,
+            strides, bt.stride(0), status.data_ptr() if status is not None else None,
+            _stream_ptr(dev))
+    _native.check(rc, "lf_paged_gather_bf16")
+    return out
