@@ -1,0 +1,92 @@
+"""End to end on the GPU through the drop-in front door: torch.compile(fn,
+backend=loopfuse_backend) versus the same function run eagerly in fp32 on the CPU - the way the
+reference's tests/test_accuracy.py:13-26 checks itself, with the 2e-2 bf16 tolerance."""
+import dataclasses
+
+import pytest
+import torch
+
+from loopfuse_b200 import loopfuse_backend
+from loopfuse_b200.variants import WORKLOADS, make_inputs
+from oracle import attention_oracle as O
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+
+
+def compile_and_run(fn, inputs):
+    torch._dynamo.reset()
+    dev_inputs = tuple(t.to("cuda") for t in inputs)
+    torch._dynamo.mark_static(dev_inputs[0], 3)
+    torch._dynamo.mark_dynamic(dev_inputs[0], 2)
+    out = torch.compile(fn, backend=loopfuse_backend, dynamic=True)(*dev_inputs)
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.parametrize("name,batch,seq", [
+    ("causal_tiny", 2, 512), ("causal_softcap", 1, 1024), ("window_gqa_softcap", 1, 1024),
+    ("decode", 4, 2048), ("paged_decode_gqa", 4, 2048),
+])
+def test_compiled_variant_matches_eager_fp32(name, batch, seq):
+    w = dataclasses.replace(WORKLOADS[name], B=batch, S=seq)
+    inputs = make_inputs(w)
+    out = compile_and_run(w.fn(), inputs)
+    want = O.workload_ref(w, inputs)
+    assert out.dtype == torch.bfloat16 and out.shape == want.shape
+    assert (out.float().cpu() - want).abs().max().item() <= TOL
+
+
+def test_compiled_function_equals_own_eager_ops_on_gpu():
+    """The package's eager custom ops (what runs without torch.compile) against the compiled
+    kernels, both on the GPU, ragged length as in the reference's S=593 case."""
+    w = dataclasses.replace(WORKLOADS["causal_tiny"], B=4, Hq=8, Hkv=8, S=593)
+    inputs = make_inputs(w)
+    out = compile_and_run(w.fn(), inputs)
+    eager = w.fn()(*(t.to("cuda").float() for t in inputs))
+    assert (out.float() - eager).abs().max().item() <= TOL
+
+
+def test_reference_style_gqa_test_shape():
+    # tests/test_accuracy.py:146-169: B4 Hq8 Hk4 S1024 D64, causal GQA via repeat_interleave
+    def fn(Q, K, V):
+        Hq, Hk = Q.shape[1], K.shape[1]
+        K = K.repeat_interleave(Hq // Hk, dim=1)
+        V = V.repeat_interleave(Hq // Hk, dim=1)
+        QK = Q @ K.transpose(-2, -1) * (Q.shape[-1] ** -0.5)
+        return torch.softmax(torch.ops.loopfuse.causal_mask(QK), dim=-1) @ V
+
+    g = torch.Generator().manual_seed(5)
+    Q = torch.randn(4, 8, 1024, 64, generator=g).bfloat16()
+    K = torch.randn(4, 4, 1024, 64, generator=g).bfloat16()
+    V = torch.randn(4, 4, 1024, 64, generator=g).bfloat16()
+    out = compile_and_run(fn, (Q, K, V))
+    want = O.attention_ref(Q, K, V, mask="causal", batch_chunk=4)
+    assert (out.float().cpu() - want).abs().max().item() <= TOL
+
+
+def test_reference_style_paged_prefill():
+    # tests/test_accuracy.py:253-278: paged K (one token per page) with a causal prefill
+    def fn(Q, K_cache, K_block_table, V):
+        K = torch.ops.loopfuse.paged_load(K_cache, K_block_table).transpose(1, 2)
+        QK = Q @ K.transpose(-2, -1) * (Q.shape[-1] ** -0.5)
+        return torch.softmax(torch.ops.loopfuse.causal_mask(QK), dim=-1) @ V
+
+    g = torch.Generator().manual_seed(6)
+    B, H, S_, D = 2, 4, 384, 64
+    Kc = torch.randn(B * S_ * 2, H, D, generator=g).bfloat16()
+    bt = torch.randint(0, B * S_ * 2, (B, S_), generator=g, dtype=torch.int32)
+    Q = torch.randn(B, H, S_, D, generator=g).bfloat16()
+    V = torch.randn(B, H, S_, D, generator=g).bfloat16()
+    with pytest.raises(Exception):
+        # K paged but V dense is outside what the binder supports; it must raise, not fall back
+        compile_and_run(fn, (Q, Kc, bt, V))
+
+
+def test_cpu_tensors_fail_loudly():
+    w = dataclasses.replace(WORKLOADS["causal_tiny"], B=1, S=128)
+    inputs = make_inputs(w)
+    torch._dynamo.reset()
+    fn = torch.compile(w.fn(), backend=loopfuse_backend, dynamic=True)
+    with pytest.raises(Exception, match="CUDA"):
+        fn(*inputs)
