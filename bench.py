@@ -114,15 +114,14 @@ def physical_gpu_index(local_rank: int) -> int:
 # --------------------------------------------------------------------------------------------
 # CPU arm: the eager fp32 computation (oracle port of the reference's eager path)
 # --------------------------------------------------------------------------------------------
-def cpu_sample(workload, heads: int = 8):
-    """Bounded sample of a workload for the CPU: one batch element, `heads` query heads."""
+def cpu_sample(workload):
+    """Bounded sample of a workload for the CPU arm. The eager fp32 computation of the headline
+    prefill configuration takes a few seconds on a multi-core host, so the sample is the whole
+    configuration there; decode samples 16 sequences (KV upcast to fp32 costs memory)."""
     import dataclasses
-    hq = min(heads, workload.Hq)
-    hkv = max(1, hq // workload.group)
-    hq = hkv * workload.group
-    if workload.kind == "paged_decode":
-        return dataclasses.replace(workload, B=1)
-    return dataclasses.replace(workload, B=1, Hq=hq, Hkv=hkv)
+    if workload.kind == "prefill":
+        return workload
+    return dataclasses.replace(workload, B=min(workload.B, 16))
 
 
 def time_cpu(workload, steps: int, warmup: int) -> dict:
