@@ -156,6 +156,25 @@ int lf_decode_paged_bf16(const LfDecodeArgs* args, void* stream);
 int lf_decode_auto_splits(int32_t B, int32_t Hkv, int32_t G, int32_t Skv, int32_t D);
 size_t lf_decode_workspace_bytes(int32_t B, int32_t Hkv, int32_t G, int32_t D, int32_t splits);
 
+/* Decode for callers that cannot allocate. No counterpart in the reference (it has neither
+ * split-KV nor a workspace). Same arguments and result as lf_decode_bf16, except that
+ * `workspace` / `workspace_bytes` are ignored: the split-KV partials go to a fixed array of
+ * LF_STATIC_SCRATCH_BYTES that is part of the library image (each GPU that loads the library
+ * holds it until the process exits). Meant for hosts that may not call cudaMalloc at launch
+ * time - a serving loop with a frozen memory pool, a plugin called from inside another
+ * runtime - and only own their input and output buffers.
+ *   - Nothing is allocated or freed, by this call or by anything it calls.
+ *   - A problem whose partials (lf_decode_workspace_bytes for the resolved split count) exceed
+ *     LF_STATIC_SCRATCH_BYTES is refused with LF_ERR_TOO_LARGE; pass a smaller `splits`.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array. Its old contents never matter (every partial
+ *     that is read was written by the same call), but two calls that run on the GPU at the
+ *     same time - different streams, or different threads - overwrite each other's partials:
+ *     keep calls on one device ordered. */
+#define LF_STATIC_SCRATCH_BYTES (8u << 20)
+int lf_decode_bf16_static(const LfDecodeArgs* args, void* stream);
+
 /* Merge split-KV partials: part_o fp32 [units, splits, D], part_ml fp32 [units, splits, 2]
  * (running max in log2 domain, sum) -> out bf16 rows; out row u lives at
  * out + (u / G / Hkv) * o_stride[0] + ((u / G) % Hkv) * o_stride[1] + (u % G) * o_stride[2]. */

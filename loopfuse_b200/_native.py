@@ -16,7 +16,10 @@ EXPORTS = [
     "lf_query", "lf_strerror", "lf_last_cuda_error", "lf_prefill_bf16", "lf_skip_range",
     "lf_decode_bf16", "lf_decode_paged_bf16", "lf_decode_auto_splits",
     "lf_decode_workspace_bytes", "lf_combine_f32", "lf_paged_gather_bf16",
+    "lf_decode_bf16_static",
 ]
+
+LF_STATIC_SCRATCH_BYTES = 8 << 20
 
 
 class LfPrefillArgs(C.Structure):
@@ -80,7 +83,7 @@ def load() -> C.CDLL:
     lib.lf_prefill_bf16.restype = C.c_int
     lib.lf_skip_range.argtypes = [C.c_int32] * 8 + [C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     lib.lf_skip_range.restype = None
-    for name in ("lf_decode_bf16", "lf_decode_paged_bf16"):
+    for name in ("lf_decode_bf16", "lf_decode_paged_bf16", "lf_decode_bf16_static"):
         fn = getattr(lib, name)
         fn.argtypes = [C.POINTER(LfDecodeArgs), C.c_void_p]
         fn.restype = C.c_int

@@ -17,6 +17,8 @@
 
 #include <math.h>
 
+#include <mutex>
+
 namespace lf {
 
 constexpr int kDecodeWarps = 4;
@@ -579,3 +581,71 @@ int lf_paged_gather_bf16(const void* pool, const int32_t* block_table, void* out
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// Decode without any allocation by the caller or the library.
+//
+// Some callers cannot call cudaMalloc or hand over a workspace at the point where they launch
+// decode: a serving loop that has frozen its memory pool, a plugin running inside another
+// runtime's callback where allocation is forbidden, or a host that only holds the input and
+// output buffers it was given. For them the split-KV partials live in this fixed array, which
+// is part of the library image: every GPU that loads the library holds these bytes until the
+// process exits.
+// ---------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_scratch[LF_STATIC_SCRATCH_BYTES];
+
+namespace lf {
+
+constexpr int kMaxStaticDevices = 64;
+static std::mutex g_static_mutex;
+static void* g_static_scratch_addr[kMaxStaticDevices] = {};
+
+// Device address of the scratch array on the current device. `g_static_scratch` itself is only
+// a host-side handle in host code, so it is translated once per device (with that device
+// current) and the translated pointer is what the kernels receive.
+static int static_scratch_address(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    set_cuda_error(e, "cudaGetDevice");
+    return LF_ERR_NO_DEVICE;
+  }
+  if (dev < 0 || dev >= kMaxStaticDevices) return LF_ERR_TOO_LARGE;
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (!g_static_scratch_addr[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || !ptr) {
+      set_cuda_error(e, "cudaGetSymbolAddress(g_static_scratch)");
+      cudaGetLastError();
+      return LF_ERR_CUDA;
+    }
+    g_static_scratch_addr[dev] = ptr;
+  }
+  *out = g_static_scratch_addr[dev];
+  return LF_OK;
+}
+
+}  // namespace lf
+
+extern "C" int lf_decode_bf16_static(const LfDecodeArgs* args, void* stream) {
+  if (!args) return LF_ERR_INVALID_ARG;
+  if (args->B <= 0 || args->Hkv <= 0 || args->G <= 0 || args->Skv <= 0)
+    return LF_ERR_INVALID_ARG;
+  // Resolve the split count exactly as lf_decode_bf16 will, then size the partials.
+  int splits = args->splits;
+  if (splits < 0) return LF_ERR_INVALID_ARG;
+  if (splits == 0) splits = lf::choose_splits(args->B, args->Hkv, args->G, args->Skv, args->D);
+  const int chunk = lf::round_up((args->Skv + splits - 1) / splits, 64);
+  splits = (args->Skv + chunk - 1) / chunk;
+  const size_t need = lf_decode_workspace_bytes(args->B, args->Hkv, args->G, args->D, splits);
+  if (need > static_cast<size_t>(LF_STATIC_SCRATCH_BYTES)) return LF_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  const int rc = lf::static_scratch_address(&scratch);
+  if (rc != LF_OK) return rc;
+  LfDecodeArgs local = *args;
+  local.splits = splits;
+  local.workspace = scratch;
+  local.workspace_bytes = static_cast<size_t>(LF_STATIC_SCRATCH_BYTES);
+  return lf::decode_impl(&local, stream, false);
+}
