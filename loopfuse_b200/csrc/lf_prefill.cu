@@ -46,6 +46,8 @@ struct StagesFor {
 };
 constexpr float kLog2eF = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 domain
+// |x| up to which tanh(x) is evaluated by its degree-7 odd polynomial (abs. error < 6e-6)
+constexpr float kTanhPolyLimit = 0.4f;
 
 constexpr int kModeNone = 0;     // logit2 = raw * c2
 constexpr int kModeSoftcap = 1;  // logit2 = tanh(raw * a) * c2
@@ -75,6 +77,33 @@ struct __align__(8) PrefillBarriers {
   uint32_t tmem_base;
   uint32_t pad;
 };
+
+// Optional phase tracing (compiled in only with -DLF_TRACE): the first CTA's role threads log
+// (event id, SM clock) pairs into `dbg_ranges`, which then must hold 4 * 2048 int64 values.
+#ifdef LF_TRACE
+struct Tracer {
+  long long* buf;
+  int n;
+  __device__ __forceinline__ void ev(int id) {
+    if (buf && n < 1023) {
+      buf[2 * n] = id;
+      buf[2 * n + 1] = clock64();
+      ++n;
+    }
+  }
+};
+#define LF_TRACE_DECL(role)                                                                   \
+  Tracer tracer{(blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && p.dbg_ranges)       \
+                    ? reinterpret_cast<long long*>(p.dbg_ranges) + (role) * 2048              \
+                    : nullptr,                                                                \
+                0}
+#define LF_TRACE_EV(id) tracer.ev(id)
+#define LF_TRACE_END() do { if (tracer.buf) { tracer.buf[2 * tracer.n] = -1; } } while (0)
+#else
+#define LF_TRACE_DECL(role)
+#define LF_TRACE_EV(id)
+#define LF_TRACE_END()
+#endif
 
 __device__ __forceinline__ void report_timeout(int32_t* status, int where) {
   if (status) atomicCAS(status, LF_DEV_OK, LF_DEV_TIMEOUT | (where << 8));
@@ -171,15 +200,18 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       }
       int n = 0;
       bool ok = true;
+      LF_TRACE_DECL(3);
       for (int j = lo; j < hi && ok; ++j) {
         for (int which = 0; which < 2 && ok; ++which, ++n) {
           const int stage = n % kStages;
           const uint32_t parity = ((n / kStages) & 1) ^ 1;
+          LF_TRACE_EV(1);
           if (!mbar_wait(&bars->kv_empty[stage], parity)) {
             report_timeout(p.status, 1);
             ok = false;
             break;
           }
+          LF_TRACE_EV(2);
           mbar_arrive_expect_tx(&bars->kv_full[stage], kTileBytes);
           const CUtensorMap* tm = which == 0 ? &tmap_k : &tmap_v;
 #pragma unroll
@@ -188,11 +220,14 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
                         kb * 64, j * kTileK, hkv, b);
         }
       }
+      LF_TRACE_END();
     }
   } else if (warp == 9) {
     // ---------------- MMA issuer ----------------
     if (lane == 0 && hi > lo) {
       bool ok = true;
+      LF_TRACE_DECL(2);
+      LF_TRACE_EV(0);
       for (int t = 0; t < 2 && ok; ++t) {
         if (has_work[t] && !mbar_wait(&bars->q_full[t], 0)) {
           report_timeout(p.status, 2);
@@ -243,6 +278,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       for (int j = lo; j < hi && ok; ++j) {
         const int nv = 2 * (j - lo) + 1;
         const int sv = nv % kStages;
+        LF_TRACE_EV(10);
         if (!mbar_wait(&bars->kv_full[sv], (nv / kStages) & 1)) {
           report_timeout(p.status, 4);
           break;
@@ -255,24 +291,30 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
           break;
         }
         tc_fence_after();
+        LF_TRACE_EV(11);
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (active(t, j)) {
+            LF_TRACE_EV(12 + 4 * t);
             if (!mbar_wait(&bars->p_full[t], kcount[t] & 1)) {
               report_timeout(p.status, 6 + t);
               ok = false;
               break;
             }
             tc_fence_after();
+            LF_TRACE_EV(13 + 4 * t);
             issue_pv(t, sv, kcount[t] > 0);
+            LF_TRACE_EV(14 + 4 * t);
             ++kcount[t];
             if (j == hi_t[t] - 1) tc_commit(&bars->o_final[t]);
           }
           if (t == 1) tc_commit(&bars->kv_empty[sv]);
           if (nxt && active(t, j + 1)) issue_qk(t, sk);
+          LF_TRACE_EV(15 + 4 * t);
         }
         if (ok && nxt) tc_commit(&bars->kv_empty[sk]);
       }
+      LF_TRACE_END();
     }
   } else {
     // ---------------- softmax warps ----------------
@@ -283,11 +325,13 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     const uint32_t s_addr = tmem_base + lane_addr + (t == 0 ? kColS0 : kColS1);
     const uint32_t o_addr = tmem_base + lane_addr + (t == 0 ? kColO0 : kColO1);
 
+#ifndef LF_TRACE
     if (p.dbg_ranges && tile_valid[t] && row == 0) {
       const int64_t idx = ((static_cast<int64_t>(b) * p.Hq + h) * p.n_qtiles + (iq0 + t)) * 2;
       p.dbg_ranges[idx] = lo_t[t];
       p.dbg_ranges[idx + 1] = hi_t[t];
     }
+#endif
 
     if (has_work[t]) {
       // Visible column interval of this row: [c_lo, c_hi].
@@ -301,51 +345,88 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       float l_run = 0.f;
       bool ok = true;
       const int nblk = hi_t[t] - lo_t[t];
+#ifdef LF_TRACE
+      Tracer tracer{(blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && p.dbg_ranges &&
+                     (warp & 3) == 0 && lane == 0)
+                        ? reinterpret_cast<long long*>(p.dbg_ranges) + t * 2048
+                        : nullptr,
+                    0};
+#endif
       for (int k = 0; k < nblk; ++k) {
         const int c0 = (lo_t[t] + k) * kTileK;
+        LF_TRACE_EV(20);
         if (!mbar_wait(&bars->s_full[t], k & 1)) {
           report_timeout(p.status, 8 + t);
           ok = false;
           break;
         }
         tc_fence_after();
+        LF_TRACE_EV(21);
+        // Raw scores of this row: 128 fp32 values, fetched in two halves so that the row-max
+        // pass over the first half overlaps the load of the second.
         uint32_t sr[4][32];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(s_addr + c * 32, sr[c]);
+        tmem_ld_32x32b_x32(s_addr, sr[0]);
+        tmem_ld_32x32b_x32(s_addr + 32, sr[1]);
         tmem_wait_ld();
+        tmem_ld_32x32b_x32(s_addr + 64, sr[2]);
+        tmem_ld_32x32b_x32(s_addr + 96, sr[3]);
 
-        // Score function (before the log2e-scaled multiplier c2).
-        if constexpr (MODE == kModeSoftcap) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c)
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              sr[c][i] = __float_as_uint(tanh_approx(__uint_as_float(sr[c][i]) * p.a));
-        } else if constexpr (MODE == kModeGeneric) {
+        const int rel_lo = c_lo - c0;  // visible columns of this row inside the tile:
+        const int rel_hi = c_hi - c0;  // [rel_lo, rel_hi]
+        const bool masked = rel_lo > 0 || rel_hi < kTileK - 1;
+
+        if constexpr (MODE == kModeGeneric) {
+          tmem_wait_ld();
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i)
               sr[c][i] = __float_as_uint(apply_mods(p.mods, __uint_as_float(sr[c][i]) * p.a));
         }
-        // Mask only on tiles that cross the row's visible interval.
-        const int rel_lo = c_lo - c0;
-        const int rel_hi = c_hi - c0;
-        if (rel_lo > 0 || rel_hi < kTileK - 1) {
+
+        // Pass 1: row max (and min, for the softcap range check), four independent chains.
+        float mxa[4], mna[4];
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 4; ++c) {
+          if (c == 2 && MODE != kModeGeneric) tmem_wait_ld();
+          mxa[c] = -INFINITY;
+          mna[c] = INFINITY;
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float v0 = __uint_as_float(sr[c][i]), v1 = __uint_as_float(sr[c][i + 1]);
+            mxa[c] = max3(mxa[c], v0, v1);
+            if constexpr (MODE == kModeSoftcap) mna[c] = min3(mna[c], v0, v1);
+          }
+        }
+        float mx_keep = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
+        LF_TRACE_EV(22);
+        if (masked) {  // max over the visible columns only
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            mxa[c] = -INFINITY;
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const int cc = c * 32 + i;
-              if (cc < rel_lo || cc > rel_hi) sr[c][i] = 0xff800000u;  // -inf
+              const float v = (cc >= rel_lo && cc <= rel_hi) ? __uint_as_float(sr[c][i]) : -INFINITY;
+              mxa[c] = fmaxf(mxa[c], v);
             }
+          }
+          mx_keep = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
         }
-        float mx = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sr[c][i]));
-        const float m_new = fmaxf(m_used, mx * p.c2);
+
+        // The score function is monotonic for the plain and softcap modes, so the max of the
+        // scores is the score of the max.
+        float tmax = mx_keep;
+        bool poly_ok = false;
+        if constexpr (MODE == kModeSoftcap) {
+          tmax = (mx_keep == -INFINITY) ? -INFINITY : tanh_approx(mx_keep * p.a);
+          // tanh by polynomial when every |x| of the warp's rows is small (else MUFU tanh)
+          const float mx_all = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
+          const float mn_all = fminf(fminf(mna[0], mna[1]), fminf(mna[2], mna[3]));
+          const float bound = fabsf(p.a) * fmaxf(fabsf(masked ? INFINITY : mx_all), fabsf(mn_all));
+          poly_ok = __all_sync(0xffffffffu, bound <= kTanhPolyLimit);
+        }
+        const float m_new = fmaxf(m_used, tmax * p.c2);
 
         // Lazy rescale: move the reference max only when it grew by more than 2^8.
         float alpha = 1.f;
@@ -368,24 +449,85 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
           }
         }
         const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-        float psum = 0.f;
+        LF_TRACE_EV(23);
+
+        // Pass 2: p = exp2(score * c2 - m), two elements per packed instruction.
+        const uint64_t neg_m2 = pack2(-m_safe, -m_safe);
+        uint64_t psum2[4] = {0ull, 0ull, 0ull, 0ull};
         uint32_t pk[2][32];
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c][i]), p.c2, -m_safe));
-            const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c][i + 1]), p.c2, -m_safe));
-            psum += p0 + p1;
-            pk[c >> 1][(c & 1) * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
+        auto finish_pair = [&](uint64_t z2, int c, int i, bool apply_mask) {
+          float z0, z1;
+          unpack2(z2, z0, z1);
+          if (apply_mask) {
+            const int cc = c * 32 + i;
+            if (cc < rel_lo || cc > rel_hi) z0 = -INFINITY;
+            if (cc + 1 < rel_lo || cc + 1 > rel_hi) z1 = -INFINITY;
           }
+          const float p0 = ex2_approx(z0), p1 = ex2_approx(z1);
+          psum2[c] = add2(psum2[c], pack2(p0, p1));
+          pk[c >> 1][(c & 1) * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
+        };
+        if (MODE == kModeSoftcap && poly_ok) {
+          // tanh(x) = x * (1 + y*(-1/3 + y*(2/15 + y*(-17/315)))), y = x^2, x = a * raw; the
+          // powers of a are folded into the coefficients so the polynomial runs on raw^2.
+          const float a2 = p.a * p.a;
+          const uint64_t b1 = pack2(-a2 / 3.f, -a2 / 3.f);
+          const uint64_t b2 = pack2(a2 * a2 * (2.f / 15.f), a2 * a2 * (2.f / 15.f));
+          const uint64_t b3 = pack2(a2 * a2 * a2 * (-17.f / 315.f), a2 * a2 * a2 * (-17.f / 315.f));
+          const uint64_t one2 = pack2(1.f, 1.f);
+          const uint64_t ac2 = pack2(p.a * p.c2, p.a * p.c2);
+          auto body = [&](bool apply_mask) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const uint64_t r2 = pack2u(sr[c][i], sr[c][i + 1]);
+                const uint64_t y2 = mul2(r2, r2);
+                uint64_t q2 = fma2(y2, b3, b2);
+                q2 = fma2(q2, y2, b1);
+                q2 = fma2(q2, y2, one2);
+                finish_pair(fma2(mul2(r2, ac2), q2, neg_m2), c, i, apply_mask);
+              }
+          };
+          if (masked) body(true); else body(false);
+        } else if constexpr (MODE == kModeSoftcap) {
+          const uint64_t c22 = pack2(p.c2, p.c2);
+          auto body = [&](bool apply_mask) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const float t0 = tanh_approx(__uint_as_float(sr[c][i]) * p.a);
+                const float t1 = tanh_approx(__uint_as_float(sr[c][i + 1]) * p.a);
+                finish_pair(fma2(pack2(t0, t1), c22, neg_m2), c, i, apply_mask);
+              }
+          };
+          if (masked) body(true); else body(false);
+        } else {
+          const uint64_t c22 = pack2(p.c2, p.c2);
+          auto body = [&](bool apply_mask) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; i += 2)
+                finish_pair(fma2(pack2u(sr[c][i], sr[c][i + 1]), c22, neg_m2), c, i, apply_mask);
+          };
+          if (masked) body(true); else body(false);
+        }
+        float ps[8];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) unpack2(psum2[c], ps[2 * c], ps[2 * c + 1]);
+        const float psum = ((ps[0] + ps[1]) + (ps[2] + ps[3])) + ((ps[4] + ps[5]) + (ps[6] + ps[7]));
         l_run = l_run * alpha + psum;
+        LF_TRACE_EV(24);
         tmem_st_32x32b_x32(s_addr, pk[0]);
         tmem_st_32x32b_x32(s_addr + 32, pk[1]);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&bars->p_full[t]);
+        LF_TRACE_EV(25);
       }
+      LF_TRACE_EV(26);
 
       // Epilogue: O_t / l -> bf16 -> global (one row per thread).
       if (ok) {
@@ -420,6 +562,8 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
           }
         }
       }
+      LF_TRACE_EV(27);
+      LF_TRACE_END();
     } else if (tile_valid[t] && grow < p.Sq) {
       // No visible key at all for this tile: softmax of an all -inf row is NaN in the
       // eager computation, so the rows are written as NaN.
