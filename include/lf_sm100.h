@@ -74,7 +74,7 @@ typedef enum {
 
 /* Prefill tile shape the sm_100a kernel uses; skip ranges are defined on it. */
 #define LF_PREFILL_TILE_Q 128
-#define LF_PREFILL_TILE_K 128
+#define LF_PREFILL_TILE_K 64
 
 typedef struct {
   const void* q;      /* bf16 [B, Hq,  Sq,  D], innermost stride 1 */
@@ -94,8 +94,8 @@ typedef struct {
   int32_t window;       /* for LF_MASK_CAUSAL_WINDOW */
   int32_t causal_offset;/* 0 for square scores */
   int32_t* status;      /* optional device word */
-  int32_t* dbg_ranges;  /* optional device int32 [B*Hq*ceil(Sq/128)*2]: the (lo,hi) KV-tile
-                           range each q-tile actually iterated, for the bit-exact check */
+  int32_t* dbg_ranges;  /* optional device int32 [B*Hq*ceil(Sq/128)*2]: the (lo,hi) range of
+                           64-key KV tiles each q-tile actually iterated (bit-exact check) */
 } LfPrefillArgs;
 
 typedef struct {

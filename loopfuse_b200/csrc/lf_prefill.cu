@@ -1,26 +1,28 @@
 // Prefill attention for sm_100a: TMA-staged tiles, tcgen05 MMA with accumulators in tensor
 // memory, online softmax in registers.
 //
-// One CTA owns two consecutive 128-row query tiles of one (batch, q head) and walks the KV
-// tiles that the skip range leaves (fully masked tiles are never loaded or multiplied).
+// One CTA owns two consecutive 128-row query tiles of one (batch, q head) and walks the 64-key
+// KV tiles that the skip range leaves (fully masked tiles are never loaded or multiplied).
 //
 //   warps 0-3   softmax for query tile 0 (one thread per score row)
 //   warps 4-7   softmax for query tile 1
-//   warp  8     TMA producer: Q tiles once, then K(j), V(j), K(j+1), ... into a ring
-//   warp  9     MMA issuer (one thread): S_t = Q_t K^T, O_t += P_t V
+//   warp  8     TMA producer: Q tiles once, then K/V tiles into a ring, in the order the MMA
+//               warp consumes them: K(lo), K(lo+1), V(lo), K(lo+2), V(lo+1), ...
+//   warp  9/10  MMA issuers (one thread each, one per query tile): S_t[buf] = Q_t K^T,
+//               O_t += P_t V
 //
 // Tensor memory (512 columns x 128 lanes of 32 bit):
-//   [0,128)    S_0 (fp32); P_0 (bf16, two per column) overwrites columns [0,64)
-//   [128,256)  S_1 / P_1
-//   [256,256+D) O_0     [384,384+D) O_1
+//   tile t, buffer b: S at column t*128 + b*64 (64 fp32 columns); P (bf16, two per column)
+//   overwrites the first 32 columns of its S buffer.   O_t at column 256 + t*128 (D columns).
 //
-// The two query tiles ping-pong on the tensor pipe: while the softmax warps of one tile turn
-// S into P, the MMA thread runs the other tile's PV and next QK^T. MMAs complete in issue
-// order, so "S_t(k) is ready" also means "O_t holds every PV up to k-1"; the softmax warps
-// use that to rescale O_t in place (only when the running max moved by more than 2^8).
+// S is double-buffered per query tile: QK^T of KV tile j+2 is issued right after PV of tile j,
+// so the tensor pipe computes the next scores while the softmax warps work on the current
+// ones; the only dependency left between the two sides is "PV(j) needs P(j)". The softmax warps
+// rescale O_t in place when the running max moves by more than 2^8 (rare); for that they wait
+// on `pv_done`, which the MMA warp commits after every PV.
 //
 // Shared-memory tiles use the 128-byte swizzle that TMA writes and the MMA descriptors read:
-// a [128 rows][D] bf16 tile is stored as D/64 blocks of [128][64] (128-byte rows).
+// a [rows][D] bf16 tile is stored as D/64 blocks of [rows][64] (128-byte rows).
 // No cluster launch and no multicast: every CTA fetches its own tiles; L2 provides the reuse
 // between the CTAs of one kv head.
 #include "lf_common.cuh"
@@ -36,18 +38,21 @@ namespace lf {
 
 constexpr int kTileQ = LF_PREFILL_TILE_Q;
 constexpr int kTileK = LF_PREFILL_TILE_K;
-constexpr int kPrefillThreads = 320;
-constexpr int kMaxStages = 8;
-// K/V ring depth: 4 x 32 KB tiles at D=128, 8 x 16 KB at D=64 (which also keeps the CTA above
+static_assert(kTileQ == 128 && kTileK == 64, "the kernel is written for 128 x 64 tiles");
+constexpr int kPrefillThreads = 352;
+constexpr int kMaxStages = 16;
+// K/V ring depth: 8 x 16 KB tiles at D=128, 16 x 8 KB at D=64 (which also keeps the CTA above
 // half of the shared memory, so two CTAs never compete for the 512 tensor-memory columns).
 template <int D>
 struct StagesFor {
-  static constexpr int value = D == 64 ? 8 : 4;
+  static constexpr int value = D == 64 ? 16 : 8;
 };
 constexpr float kLog2eF = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 domain
-// |x| up to which tanh(x) is evaluated by its degree-7 odd polynomial (abs. error < 6e-6)
-constexpr float kTanhPolyLimit = 0.4f;
+// tanh(x) by odd polynomial: x*(1 - x^2/3) up to |x| <= 0.125 (abs. error < 4.1e-6), degree 7
+// up to |x| <= 0.4 (abs. error < 6e-6); MUFU tanh beyond.
+constexpr float kTanhPoly1Limit = 0.125f;
+constexpr float kTanhPoly3Limit = 0.4f;
 
 constexpr int kModeNone = 0;     // logit2 = raw * c2
 constexpr int kModeSoftcap = 1;  // logit2 = tanh(raw * a) * c2
@@ -71,9 +76,10 @@ struct __align__(8) PrefillBarriers {
   uint64_t q_full[2];
   uint64_t kv_full[kMaxStages];
   uint64_t kv_empty[kMaxStages];
-  uint64_t s_full[2];
-  uint64_t p_full[2];
-  uint64_t o_final[2];
+  uint64_t s_full[2][2];   // [tile][buffer]  MMA -> softmax
+  uint64_t p_full[2][2];   // [tile][buffer]  softmax -> MMA
+  uint64_t pv_done[2];     // [tile] one completion per PV
+  uint64_t o_final[2];     // [tile] last PV done
   uint32_t tmem_base;
   uint32_t pad;
 };
@@ -92,15 +98,16 @@ struct Tracer {
     }
   }
 };
-#define LF_TRACE_DECL(role)                                                                   \
-  Tracer tracer{(blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && p.dbg_ranges)       \
+#define LF_TRACE_DECL(role, cond)                                                             \
+  Tracer tracer{(blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && p.dbg_ranges &&     \
+                 (cond))                                                                      \
                     ? reinterpret_cast<long long*>(p.dbg_ranges) + (role) * 2048              \
                     : nullptr,                                                                \
                 0}
 #define LF_TRACE_EV(id) tracer.ev(id)
 #define LF_TRACE_END() do { if (tracer.buf) { tracer.buf[2 * tracer.n] = -1; } } while (0)
 #else
-#define LF_TRACE_DECL(role)
+#define LF_TRACE_DECL(role, cond)
 #define LF_TRACE_EV(id)
 #define LF_TRACE_END()
 #endif
@@ -115,19 +122,21 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
                    const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
   constexpr int kStages = StagesFor<D>::value;
-  constexpr int kBlocksD = D / 64;                  // 64-column swizzle blocks per tile row
-  constexpr uint32_t kBlockBytes = kTileQ * 128;    // one [128][64] bf16 block
-  constexpr uint32_t kTileBytes = kBlockBytes * kBlocksD;
+  constexpr int kBlocksD = D / 64;                    // 64-column swizzle blocks per tile row
+  constexpr uint32_t kQBlockBytes = kTileQ * 128;     // one [128][64] bf16 block of Q
+  constexpr uint32_t kQTileBytes = kQBlockBytes * kBlocksD;
+  constexpr uint32_t kKVBlockBytes = kTileK * 128;    // one [64][64] bf16 block of K or V
+  constexpr uint32_t kKVTileBytes = kKVBlockBytes * kBlocksD;
   constexpr uint32_t kIdescQK = make_idesc_bf16(128, kTileK, 0);
   constexpr uint32_t kIdescPV = make_idesc_bf16(128, D, 1);
-  constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
+  constexpr uint32_t kColO = 256;
 
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~static_cast<uintptr_t>(1023));
   PrefillBarriers* bars = reinterpret_cast<PrefillBarriers*>(smem);
   unsigned char* sQ = smem + 1024;
-  unsigned char* sKV = sQ + 2 * kTileBytes;
+  unsigned char* sKV = sQ + 2 * kQTileBytes;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -164,11 +173,14 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     mbar_init(&bars->q_full[1], 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&bars->kv_full[s], 1);
-      mbar_init(&bars->kv_empty[s], 1);
+      mbar_init(&bars->kv_empty[s], 2);
     }
     for (int t = 0; t < 2; ++t) {
-      mbar_init(&bars->s_full[t], 1);
-      mbar_init(&bars->p_full[t], 128);
+      for (int bf = 0; bf < 2; ++bf) {
+        mbar_init(&bars->s_full[t][bf], 1);
+        mbar_init(&bars->p_full[t][bf], 128);
+      }
+      mbar_init(&bars->pv_done[t], 1);
       mbar_init(&bars->o_final[t], 1);
     }
     mbar_fence_init();
@@ -190,129 +202,143 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
   if (warp == 8) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
+      LF_TRACE_DECL(3, true);
       for (int t = 0; t < 2; ++t) {
         if (!has_work[t]) continue;
-        mbar_arrive_expect_tx(&bars->q_full[t], kTileBytes);
+        mbar_arrive_expect_tx(&bars->q_full[t], kQTileBytes);
 #pragma unroll
         for (int kb = 0; kb < kBlocksD; ++kb)
-          tma_load_4d(sQ + t * kTileBytes + kb * kBlockBytes, &tmap_q, &bars->q_full[t], kb * 64,
-                      (iq0 + t) * kTileQ, h, b);
+          tma_load_4d(sQ + t * kQTileBytes + kb * kQBlockBytes, &tmap_q, &bars->q_full[t],
+                      kb * 64, (iq0 + t) * kTileQ, h, b);
       }
       int n = 0;
       bool ok = true;
-      LF_TRACE_DECL(3);
-      for (int j = lo; j < hi && ok; ++j) {
-        for (int which = 0; which < 2 && ok; ++which, ++n) {
-          const int stage = n % kStages;
-          const uint32_t parity = ((n / kStages) & 1) ^ 1;
-          LF_TRACE_EV(1);
-          if (!mbar_wait(&bars->kv_empty[stage], parity)) {
-            report_timeout(p.status, 1);
-            ok = false;
-            break;
-          }
-          LF_TRACE_EV(2);
-          mbar_arrive_expect_tx(&bars->kv_full[stage], kTileBytes);
-          const CUtensorMap* tm = which == 0 ? &tmap_k : &tmap_v;
+      auto load = [&](const CUtensorMap* tm, int j) {
+        if (!ok) return;
+        const int stage = n % kStages;
+        const uint32_t parity = ((n / kStages) & 1) ^ 1;
+        ++n;
+        LF_TRACE_EV(1);
+        if (!mbar_wait(&bars->kv_empty[stage], parity)) {
+          report_timeout(p.status, 1);
+          ok = false;
+          return;
+        }
+        LF_TRACE_EV(2);
+        mbar_arrive_expect_tx(&bars->kv_full[stage], kKVTileBytes);
 #pragma unroll
-          for (int kb = 0; kb < kBlocksD; ++kb)
-            tma_load_4d(sKV + stage * kTileBytes + kb * kBlockBytes, tm, &bars->kv_full[stage],
-                        kb * 64, j * kTileK, hkv, b);
+        for (int kb = 0; kb < kBlocksD; ++kb)
+          tma_load_4d(sKV + stage * kKVTileBytes + kb * kKVBlockBytes, tm, &bars->kv_full[stage],
+                      kb * 64, j * kTileK, hkv, b);
+      };
+      if (hi > lo) {
+        load(&tmap_k, lo);
+        if (lo + 1 < hi) load(&tmap_k, lo + 1);
+        for (int j = lo; j < hi; ++j) {
+          load(&tmap_v, j);
+          if (j + 2 < hi) load(&tmap_k, j + 2);
         }
       }
       LF_TRACE_END();
     }
-  } else if (warp == 9) {
-    // ---------------- MMA issuer ----------------
+  } else if (warp == 9 || warp == 10) {
+    // ---------------- MMA issuers: warp 9 drives query tile 0, warp 10 query tile 1 ----------
+    // Two issuing threads halve the per-instruction issue overhead; the tensor pipe serialises
+    // the two independent streams. Both walk the same K/V ring and both release every stage
+    // (kv_empty counts two arrivals), whether or not their tile used it.
     if (lane == 0 && hi > lo) {
+      const int t = warp - 9;
       bool ok = true;
-      LF_TRACE_DECL(2);
+      LF_TRACE_DECL(2, t == 0);
       LF_TRACE_EV(0);
-      for (int t = 0; t < 2 && ok; ++t) {
-        if (has_work[t] && !mbar_wait(&bars->q_full[t], 0)) {
-          report_timeout(p.status, 2);
-          ok = false;
-        }
+      if (has_work[t] && !mbar_wait(&bars->q_full[t], 0)) {
+        report_timeout(p.status, 2);
+        ok = false;
       }
-      const uint32_t sQ_addr = smem_u32(sQ);
-      const uint32_t sKV_addr = smem_u32(sKV);
-      const uint32_t col_s[2] = {kColS0, kColS1};
-      const uint32_t col_o[2] = {kColO0, kColO1};
-      int kcount[2] = {0, 0};  // KV tiles issued so far per query tile
+      // Descriptors are built once; per MMA only the start-address field moves (in 16-byte
+      // units, no carry out of the 14-bit field since shared memory ends below 256 KB).
+      constexpr uint32_t kStageUnits = kKVTileBytes >> 4;
+      const uint64_t qdesc = make_smem_desc_sw128(smem_u32(sQ) + t * kQTileBytes, 16, 1024);
+      const uint64_t kdesc0 = make_smem_desc_sw128(smem_u32(sKV), 16, 1024);
+      const uint64_t vdesc0 = make_smem_desc_sw128(smem_u32(sKV), kKVBlockBytes, 1024);
+      const uint32_t s_col = tmem_base + t * 128;
+      const uint32_t o_col = tmem_base + kColO + t * 128;
+      int n = 0;  // ring position, walks the same sequence as the producer
 
-      auto active = [&](int t, int j) { return has_work[t] && j >= lo_t[t] && j < hi_t[t]; };
-      auto issue_qk = [&](int t, int stage) {
-        const uint32_t qa = sQ_addr + t * kTileBytes;
-        const uint32_t ka = sKV_addr + stage * kTileBytes;
+      auto active = [&](int j) { return has_work[t] && j >= lo_t[t] && j < hi_t[t]; };
+      auto wait_slot = [&](int where) -> int {  // next ring slot, waited full; -1 on time-out
+        const int stage = n % kStages;
+        const uint32_t parity = (n / kStages) & 1;
+        ++n;
+        if (!mbar_wait(&bars->kv_full[stage], parity)) {
+          report_timeout(p.status, where);
+          ok = false;
+          return -1;
+        }
+        return stage;
+      };
+      auto issue_qk = [&](int stage, int j) {
+        const int buf = (j - lo_t[t]) & 1;
+        const uint64_t kd = kdesc0 + static_cast<uint64_t>(stage * kStageUnits);
+        const uint32_t d = s_col + buf * 64;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks / 4) * kBlockBytes + (ks % 4) * 32;
-          mma_ss(tmem_base + col_s[t], make_smem_desc_sw128(qa + off, 16, 1024),
-                 make_smem_desc_sw128(ka + off, 16, 1024), kIdescQK, ks > 0 ? 1u : 0u);
+          mma_ss(d, qdesc + static_cast<uint64_t>((ks / 4) * (kQBlockBytes >> 4) + (ks % 4) * 2),
+                 kd + static_cast<uint64_t>((ks / 4) * (kKVBlockBytes >> 4) + (ks % 4) * 2),
+                 kIdescQK, ks > 0 ? 1u : 0u);
         }
-        tc_commit(&bars->s_full[t]);
+        tc_commit(&bars->s_full[t][buf]);
       };
-      auto issue_pv = [&](int t, int stage, bool accumulate) {
-        const uint32_t va = sKV_addr + stage * kTileBytes;
+      auto issue_pv = [&](int stage, int kt) {
+        const uint64_t vd = vdesc0 + static_cast<uint64_t>(stage * kStageUnits);
+        const uint32_t a = s_col + (kt & 1) * 64;
 #pragma unroll
         for (int ks = 0; ks < kTileK / 16; ++ks) {
-          mma_ts(tmem_base + col_o[t], tmem_base + col_s[t] + ks * 8,
-                 make_smem_desc_sw128(va + ks * 2048, kBlockBytes, 1024), kIdescPV,
-                 (accumulate || ks > 0) ? 1u : 0u);
+          mma_ts(o_col, a + ks * 8, vd + static_cast<uint64_t>(ks * (2048 >> 4)), kIdescPV,
+                 (kt > 0 || ks > 0) ? 1u : 0u);
         }
+        tc_commit(&bars->pv_done[t]);
       };
 
-      if (ok) {
-        // Prologue: first QK^T of each tile that starts at `lo`.
-        const int stage = 0;
-        if (!mbar_wait(&bars->kv_full[stage], 0)) {
-          report_timeout(p.status, 3);
-          ok = false;
-        } else {
-          tc_fence_after();
-          if (active(0, lo)) issue_qk(0, stage);
-          if (active(1, lo)) issue_qk(1, stage);
-          tc_commit(&bars->kv_empty[stage]);
-        }
+      // Prologue: scores of the first two KV tiles.
+      for (int jj = lo; jj < hi && jj < lo + 2 && ok; ++jj) {
+        const int stage = wait_slot(3);
+        if (stage < 0) break;
+        tc_fence_after();
+        if (active(jj)) issue_qk(stage, jj);
+        tc_commit(&bars->kv_empty[stage]);
       }
       for (int j = lo; j < hi && ok; ++j) {
-        const int nv = 2 * (j - lo) + 1;
-        const int sv = nv % kStages;
         LF_TRACE_EV(10);
-        if (!mbar_wait(&bars->kv_full[sv], (nv / kStages) & 1)) {
-          report_timeout(p.status, 4);
-          break;
-        }
-        const bool nxt = j + 1 < hi;
-        const int nk = nv + 1;
-        const int sk = nk % kStages;
-        if (nxt && !mbar_wait(&bars->kv_full[sk], (nk / kStages) & 1)) {
-          report_timeout(p.status, 5);
-          break;
+        const int sv = wait_slot(4);
+        if (sv < 0) break;
+        const bool k2 = j + 2 < hi;
+        int sk = 0;
+        if (k2) {
+          sk = wait_slot(5);
+          if (sk < 0) break;
         }
         tc_fence_after();
         LF_TRACE_EV(11);
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          if (active(t, j)) {
-            LF_TRACE_EV(12 + 4 * t);
-            if (!mbar_wait(&bars->p_full[t], kcount[t] & 1)) {
-              report_timeout(p.status, 6 + t);
-              ok = false;
-              break;
-            }
-            tc_fence_after();
-            LF_TRACE_EV(13 + 4 * t);
-            issue_pv(t, sv, kcount[t] > 0);
-            LF_TRACE_EV(14 + 4 * t);
-            ++kcount[t];
-            if (j == hi_t[t] - 1) tc_commit(&bars->o_final[t]);
+        if (active(j)) {
+          const int kt = j - lo_t[t];
+          if (!mbar_wait(&bars->p_full[t][kt & 1], (kt >> 1) & 1)) {
+            report_timeout(p.status, 6 + t);
+            ok = false;
+            break;
           }
-          if (t == 1) tc_commit(&bars->kv_empty[sv]);
-          if (nxt && active(t, j + 1)) issue_qk(t, sk);
-          LF_TRACE_EV(15 + 4 * t);
+          tc_fence_after();
+          LF_TRACE_EV(13);
+          issue_pv(sv, kt);
+          LF_TRACE_EV(14);
+          if (j == hi_t[t] - 1) tc_commit(&bars->o_final[t]);
         }
-        if (ok && nxt) tc_commit(&bars->kv_empty[sk]);
+        tc_commit(&bars->kv_empty[sv]);
+        if (k2) {
+          if (active(j + 2)) issue_qk(sk, j + 2);
+          tc_commit(&bars->kv_empty[sk]);
+        }
+        LF_TRACE_EV(15);
       }
       LF_TRACE_END();
     }
@@ -322,8 +348,8 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     const int row = (warp & 3) * 32 + lane;  // row inside the tile == tensor-memory lane
     const int grow = (iq0 + t) * kTileQ + row;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t s_addr = tmem_base + lane_addr + (t == 0 ? kColS0 : kColS1);
-    const uint32_t o_addr = tmem_base + lane_addr + (t == 0 ? kColO0 : kColO1);
+    const uint32_t s_base = tmem_base + lane_addr + t * 128;
+    const uint32_t o_addr = tmem_base + lane_addr + kColO + t * 128;
 
 #ifndef LF_TRACE
     if (p.dbg_ranges && tile_valid[t] && row == 0) {
@@ -345,31 +371,25 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       float l_run = 0.f;
       bool ok = true;
       const int nblk = hi_t[t] - lo_t[t];
-#ifdef LF_TRACE
-      Tracer tracer{(blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && p.dbg_ranges &&
-                     (warp & 3) == 0 && lane == 0)
-                        ? reinterpret_cast<long long*>(p.dbg_ranges) + t * 2048
-                        : nullptr,
-                    0};
-#endif
+      LF_TRACE_DECL(t, (warp & 3) == 0 && lane == 0);
       for (int k = 0; k < nblk; ++k) {
         const int c0 = (lo_t[t] + k) * kTileK;
+        const int buf = k & 1;
+        const uint32_t s_addr = s_base + buf * 64;
         LF_TRACE_EV(20);
-        if (!mbar_wait(&bars->s_full[t], k & 1)) {
+        if (!mbar_wait(&bars->s_full[t][buf], (k >> 1) & 1)) {
           report_timeout(p.status, 8 + t);
           ok = false;
           break;
         }
         tc_fence_after();
         LF_TRACE_EV(21);
-        // Raw scores of this row: 128 fp32 values, fetched in two halves so that the row-max
+        // Raw scores of this row: 64 fp32 values, fetched in two halves so that the row-max
         // pass over the first half overlaps the load of the second.
-        uint32_t sr[4][32];
+        uint32_t sr[2][32];
         tmem_ld_32x32b_x32(s_addr, sr[0]);
-        tmem_ld_32x32b_x32(s_addr + 32, sr[1]);
         tmem_wait_ld();
-        tmem_ld_32x32b_x32(s_addr + 64, sr[2]);
-        tmem_ld_32x32b_x32(s_addr + 96, sr[3]);
+        tmem_ld_32x32b_x32(s_addr + 32, sr[1]);
 
         const int rel_lo = c_lo - c0;  // visible columns of this row inside the tile:
         const int rel_hi = c_hi - c0;  // [rel_lo, rel_hi]
@@ -378,31 +398,36 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         if constexpr (MODE == kModeGeneric) {
           tmem_wait_ld();
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+          for (int c = 0; c < 2; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i)
               sr[c][i] = __float_as_uint(apply_mods(p.mods, __uint_as_float(sr[c][i]) * p.a));
         }
 
-        // Pass 1: row max (and min, for the softcap range check), four independent chains.
+        // Pass 1: row max (and min, for the softcap range check), independent chains.
         float mxa[4], mna[4];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          if (c == 2 && MODE != kModeGeneric) tmem_wait_ld();
-          mxa[c] = -INFINITY;
-          mna[c] = INFINITY;
+        for (int c = 0; c < 2; ++c) {
+          if (c == 1 && MODE != kModeGeneric) tmem_wait_ld();
+          mxa[2 * c] = mxa[2 * c + 1] = -INFINITY;
+          mna[2 * c] = mna[2 * c + 1] = INFINITY;
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
+          for (int i = 0; i < 32; i += 4) {
             const float v0 = __uint_as_float(sr[c][i]), v1 = __uint_as_float(sr[c][i + 1]);
-            mxa[c] = max3(mxa[c], v0, v1);
-            if constexpr (MODE == kModeSoftcap) mna[c] = min3(mna[c], v0, v1);
+            const float v2 = __uint_as_float(sr[c][i + 2]), v3 = __uint_as_float(sr[c][i + 3]);
+            mxa[2 * c] = max3(mxa[2 * c], v0, v1);
+            mxa[2 * c + 1] = max3(mxa[2 * c + 1], v2, v3);
+            if constexpr (MODE == kModeSoftcap) {
+              mna[2 * c] = min3(mna[2 * c], v0, v1);
+              mna[2 * c + 1] = min3(mna[2 * c + 1], v2, v3);
+            }
           }
         }
-        float mx_keep = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
-        LF_TRACE_EV(22);
+        const float mx_all = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
+        float mx_keep = mx_all;
         if (masked) {  // max over the visible columns only
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             mxa[c] = -INFINITY;
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
@@ -411,20 +436,22 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
               mxa[c] = fmaxf(mxa[c], v);
             }
           }
-          mx_keep = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
+          mx_keep = fmaxf(mxa[0], mxa[1]);
         }
+        LF_TRACE_EV(22);
 
         // The score function is monotonic for the plain and softcap modes, so the max of the
         // scores is the score of the max.
         float tmax = mx_keep;
-        bool poly_ok = false;
+        int tanh_path = 2;  // 0: x*(1 - x^2/3), 1: degree-7 polynomial, 2: MUFU tanh
         if constexpr (MODE == kModeSoftcap) {
           tmax = (mx_keep == -INFINITY) ? -INFINITY : tanh_approx(mx_keep * p.a);
-          // tanh by polynomial when every |x| of the warp's rows is small (else MUFU tanh)
-          const float mx_all = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
+          // Every |x| of the warp's rows decides (masked columns included: their raw scores
+          // are ordinary finite numbers).
           const float mn_all = fminf(fminf(mna[0], mna[1]), fminf(mna[2], mna[3]));
-          const float bound = fabsf(p.a) * fmaxf(fabsf(masked ? INFINITY : mx_all), fabsf(mn_all));
-          poly_ok = __all_sync(0xffffffffu, bound <= kTanhPolyLimit);
+          const float bound = fabsf(p.a) * fmaxf(fabsf(mx_all), fabsf(mn_all));
+          if (__all_sync(0xffffffffu, bound <= kTanhPoly1Limit)) tanh_path = 0;
+          else if (__all_sync(0xffffffffu, bound <= kTanhPoly3Limit)) tanh_path = 1;
         }
         const float m_new = fmaxf(m_used, tmax * p.c2);
 
@@ -437,6 +464,14 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
           m_used = m_new;
         }
         if (k > 0 && __any_sync(0xffffffffu, need)) {
+          // O_t must hold every PV up to k-1 and none may be in flight: PV(k-2) is known to be
+          // complete (S(k) was computed after it), so pv_done is at most one phase behind.
+          if (!mbar_wait(&bars->pv_done[t], (k - 1) & 1)) {
+            report_timeout(p.status, 12 + t);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
 #pragma unroll
           for (int c = 0; c < D / 32; ++c) {
             uint32_t orr[32];
@@ -454,7 +489,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         // Pass 2: p = exp2(score * c2 - m), two elements per packed instruction.
         const uint64_t neg_m2 = pack2(-m_safe, -m_safe);
         uint64_t psum2[4] = {0ull, 0ull, 0ull, 0ull};
-        uint32_t pk[2][32];
+        uint32_t pk[32];
         auto finish_pair = [&](uint64_t z2, int c, int i, bool apply_mask) {
           float z0, z1;
           unpack2(z2, z0, z1);
@@ -464,37 +499,52 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
             if (cc + 1 < rel_lo || cc + 1 > rel_hi) z1 = -INFINITY;
           }
           const float p0 = ex2_approx(z0), p1 = ex2_approx(z1);
-          psum2[c] = add2(psum2[c], pack2(p0, p1));
-          pk[c >> 1][(c & 1) * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
+          psum2[(c * 2 + (i >> 1)) & 3] = add2(psum2[(c * 2 + (i >> 1)) & 3], pack2(p0, p1));
+          pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
         };
-        if (MODE == kModeSoftcap && poly_ok) {
-          // tanh(x) = x * (1 + y*(-1/3 + y*(2/15 + y*(-17/315)))), y = x^2, x = a * raw; the
-          // powers of a are folded into the coefficients so the polynomial runs on raw^2.
+        if (MODE == kModeSoftcap && tanh_path < 2) {
+          // tanh(x) = x*(1 + y*(-1/3 + y*(2/15 + y*(-17/315)))), y = x^2, x = a*raw; the powers
+          // of a are folded into the coefficients so that the polynomial runs on raw^2.
           const float a2 = p.a * p.a;
           const uint64_t b1 = pack2(-a2 / 3.f, -a2 / 3.f);
-          const uint64_t b2 = pack2(a2 * a2 * (2.f / 15.f), a2 * a2 * (2.f / 15.f));
-          const uint64_t b3 = pack2(a2 * a2 * a2 * (-17.f / 315.f), a2 * a2 * a2 * (-17.f / 315.f));
           const uint64_t one2 = pack2(1.f, 1.f);
           const uint64_t ac2 = pack2(p.a * p.c2, p.a * p.c2);
-          auto body = [&](bool apply_mask) {
+          if (tanh_path == 0) {
+            auto body = [&](bool apply_mask) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+              for (int c = 0; c < 2; ++c)
 #pragma unroll
-              for (int i = 0; i < 32; i += 2) {
-                const uint64_t r2 = pack2u(sr[c][i], sr[c][i + 1]);
-                const uint64_t y2 = mul2(r2, r2);
-                uint64_t q2 = fma2(y2, b3, b2);
-                q2 = fma2(q2, y2, b1);
-                q2 = fma2(q2, y2, one2);
-                finish_pair(fma2(mul2(r2, ac2), q2, neg_m2), c, i, apply_mask);
-              }
-          };
-          if (masked) body(true); else body(false);
+                for (int i = 0; i < 32; i += 2) {
+                  const uint64_t r2 = pack2u(sr[c][i], sr[c][i + 1]);
+                  const uint64_t q2 = fma2(mul2(r2, r2), b1, one2);
+                  finish_pair(fma2(mul2(r2, ac2), q2, neg_m2), c, i, apply_mask);
+                }
+            };
+            if (masked) body(true); else body(false);
+          } else {
+            const uint64_t b2 = pack2(a2 * a2 * (2.f / 15.f), a2 * a2 * (2.f / 15.f));
+            const uint64_t b3 =
+                pack2(a2 * a2 * a2 * (-17.f / 315.f), a2 * a2 * a2 * (-17.f / 315.f));
+            auto body = [&](bool apply_mask) {
+#pragma unroll
+              for (int c = 0; c < 2; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                  const uint64_t r2 = pack2u(sr[c][i], sr[c][i + 1]);
+                  const uint64_t y2 = mul2(r2, r2);
+                  uint64_t q2 = fma2(y2, b3, b2);
+                  q2 = fma2(q2, y2, b1);
+                  q2 = fma2(q2, y2, one2);
+                  finish_pair(fma2(mul2(r2, ac2), q2, neg_m2), c, i, apply_mask);
+                }
+            };
+            if (masked) body(true); else body(false);
+          }
         } else if constexpr (MODE == kModeSoftcap) {
           const uint64_t c22 = pack2(p.c2, p.c2);
           auto body = [&](bool apply_mask) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+            for (int c = 0; c < 2; ++c)
 #pragma unroll
               for (int i = 0; i < 32; i += 2) {
                 const float t0 = tanh_approx(__uint_as_float(sr[c][i]) * p.a);
@@ -507,7 +557,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
           const uint64_t c22 = pack2(p.c2, p.c2);
           auto body = [&](bool apply_mask) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+            for (int c = 0; c < 2; ++c)
 #pragma unroll
               for (int i = 0; i < 32; i += 2)
                 finish_pair(fma2(pack2u(sr[c][i], sr[c][i + 1]), c22, neg_m2), c, i, apply_mask);
@@ -520,11 +570,10 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         const float psum = ((ps[0] + ps[1]) + (ps[2] + ps[3])) + ((ps[4] + ps[5]) + (ps[6] + ps[7]));
         l_run = l_run * alpha + psum;
         LF_TRACE_EV(24);
-        tmem_st_32x32b_x32(s_addr, pk[0]);
-        tmem_st_32x32b_x32(s_addr + 32, pk[1]);
+        tmem_st_32x32b_x32(s_addr, pk);
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(&bars->p_full[t]);
+        mbar_arrive(&bars->p_full[t][buf]);
         LF_TRACE_EV(25);
       }
       LF_TRACE_EV(26);
@@ -603,10 +652,10 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
   return fn;
 }
 
-// Tensor map over a bf16 [B, H, S, D] tensor (innermost stride 1), box = [1, 1, 128, 64],
+// Tensor map over a bf16 [B, H, S, D] tensor (innermost stride 1), box = [1, 1, box_rows, 64],
 // 128-byte swizzle, out-of-range rows read as zero.
 static int make_tile_map(CUtensorMap* map, const void* base, int B, int H, int S, int D,
-                         const int64_t* stride /* b, h, s in elements */) {
+                         const int64_t* stride /* b, h, s in elements */, int box_rows) {
   auto fn = get_encode_fn();
   if (!fn) return LF_ERR_CUDA;
   cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S),
@@ -622,7 +671,7 @@ static int make_tile_map(CUtensorMap* map, const void* base, int B, int H, int S
       else
         return LF_ERR_ALIGNMENT;
     }
-  cuuint32_t box[4] = {64, 128, 1, 1};
+  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims,
                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -637,9 +686,10 @@ static int make_tile_map(CUtensorMap* map, const void* base, int B, int H, int S
 template <int D, int MODE>
 static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                           const PrefillParams& p, int B, cudaStream_t st) {
-  constexpr size_t kTileBytes = static_cast<size_t>(kTileQ) * D * 2;
-  constexpr size_t smem = 1024 /*align slack*/ + 1024 /*barriers*/ + 2 * kTileBytes +
-                          StagesFor<D>::value * kTileBytes;
+  constexpr size_t kQTileBytes = static_cast<size_t>(kTileQ) * D * 2;
+  constexpr size_t kKVTileBytes = static_cast<size_t>(kTileK) * D * 2;
+  constexpr size_t smem = 1024 /*align slack*/ + 1024 /*barriers*/ + 2 * kQTileBytes +
+                          StagesFor<D>::value * kKVTileBytes;
   static thread_local int configured_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -736,11 +786,11 @@ static int prefill_impl(const LfPrefillArgs* a, void* stream) {
   }
 
   CUtensorMap mq, mk, mv;
-  int rc = make_tile_map(&mq, a->q, a->B, a->Hq, a->Sq, a->D, a->q_stride);
+  int rc = make_tile_map(&mq, a->q, a->B, a->Hq, a->Sq, a->D, a->q_stride, kTileQ);
   if (rc != LF_OK) return rc;
-  rc = make_tile_map(&mk, a->k, a->B, a->Hkv, a->Skv, a->D, a->k_stride);
+  rc = make_tile_map(&mk, a->k, a->B, a->Hkv, a->Skv, a->D, a->k_stride, kTileK);
   if (rc != LF_OK) return rc;
-  rc = make_tile_map(&mv, a->v, a->B, a->Hkv, a->Skv, a->D, a->v_stride);
+  rc = make_tile_map(&mv, a->v, a->B, a->Hkv, a->Skv, a->D, a->v_stride, kTileK);
   if (rc != LF_OK) return rc;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);

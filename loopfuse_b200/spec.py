@@ -33,7 +33,7 @@ MOD_NAMES = {
 }
 
 TILE_Q = 128
-TILE_K = 128
+TILE_K = 64
 
 
 @dataclasses.dataclass(frozen=True)

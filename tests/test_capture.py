@@ -42,7 +42,7 @@ def test_causal_tiny():
     assert (plan.B, plan.Hq, plan.Hkv, plan.Sq, plan.Skv, plan.D) == (2, 4, 4, 256, 256, 64)
     assert plan.scale == pytest.approx(64 ** -0.5)
     assert plan.mods == () and plan.spec.mask_kind == S.MASK_CAUSAL
-    assert plan.skip_ranges == [(0, 1), (0, 2)]
+    assert plan.skip_ranges == [(0, 2), (0, 4)]
 
 
 def test_causal_softcap():
@@ -67,7 +67,7 @@ def test_window_ranges_at_benchmark_length():
     w = dataclasses.replace(WORKLOADS["window_gqa_softcap"], B=1, Hq=4, Hkv=1, D=64)
     plan = compile_plan(w.fn(), make_inputs(w))
     assert plan.skip_ranges == S.skip_table(S.MASK_CAUSAL_WINDOW, 256, 0, 2048, 2048)
-    assert sum(hi - lo for lo, hi in plan.skip_ranges) == 45
+    assert sum(hi - lo for lo, hi in plan.skip_ranges) == 90
 
 
 def test_decode():

@@ -267,7 +267,8 @@ def test_kernel_iterates_exactly_the_analysed_skip_ranges(kind, W, S_):
     keep = O.keep_matrix(mask, W, S_, S_)
     for iq in range(n_qt):
         assert tuple(got[0, iq].tolist()) == table[iq] == tuple(got[1, iq].tolist())
-        assert table[iq] == O.brute_force_skip_range(mask, W, S_, S_, 128, 128, iq, keep=keep)
+        assert table[iq] == O.brute_force_skip_range(mask, W, S_, S_, S.TILE_Q, S.TILE_K, iq,
+                                                     keep=keep)
 
 
 def test_prefill_config2_full_size_sample():

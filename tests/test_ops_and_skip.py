@@ -112,8 +112,11 @@ def test_skip_range_vs_reference_generated_bounds(golden_dir):
 
 
 def test_live_tile_counts_at_benchmark_shapes():
-    # causal S=2048, 128x128 tiles: 136 of 256 tiles; window 256: 45 of 256
-    causal = S.skip_table(S.MASK_CAUSAL, 0, 0, 2048, 2048)
-    window = S.skip_table(S.MASK_CAUSAL_WINDOW, 256, 0, 2048, 2048)
-    assert sum(hi - lo for lo, hi in causal) == 136
-    assert sum(hi - lo for lo, hi in window) == 45
+    # causal S=2048: 136 of 256 tiles at 128x128, 272 of 512 at the kernel's 128x64;
+    # window 256: 45 of 256 and 90 of 512
+    assert (S.TILE_Q, S.TILE_K) == (128, 64)
+    for tk, n_causal, n_window in ((128, 136, 45), (64, 272, 90)):
+        causal = S.skip_table(S.MASK_CAUSAL, 0, 0, 2048, 2048, 128, tk)
+        window = S.skip_table(S.MASK_CAUSAL_WINDOW, 256, 0, 2048, 2048, 128, tk)
+        assert sum(hi - lo for lo, hi in causal) == n_causal
+        assert sum(hi - lo for lo, hi in window) == n_window
