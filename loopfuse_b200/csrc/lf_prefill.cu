@@ -384,19 +384,17 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         }
         tc_fence_after();
         LF_TRACE_EV(21);
-        // Raw scores of this row: 64 fp32 values, fetched in two halves so that the row-max
-        // pass over the first half overlaps the load of the second.
+        // Raw scores of this row: 64 fp32 values.
         uint32_t sr[2][32];
         tmem_ld_32x32b_x32(s_addr, sr[0]);
-        tmem_wait_ld();
         tmem_ld_32x32b_x32(s_addr + 32, sr[1]);
+        tmem_wait_ld();
 
         const int rel_lo = c_lo - c0;  // visible columns of this row inside the tile:
         const int rel_hi = c_hi - c0;  // [rel_lo, rel_hi]
         const bool masked = rel_lo > 0 || rel_hi < kTileK - 1;
 
         if constexpr (MODE == kModeGeneric) {
-          tmem_wait_ld();
 #pragma unroll
           for (int c = 0; c < 2; ++c)
 #pragma unroll
@@ -408,7 +406,6 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         float mxa[4], mna[4];
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          if (c == 1 && MODE != kModeGeneric) tmem_wait_ld();
           mxa[2 * c] = mxa[2 * c + 1] = -INFINITY;
           mna[2 * c] = mna[2 * c + 1] = INFINITY;
 #pragma unroll
@@ -443,27 +440,28 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         // The score function is monotonic for the plain and softcap modes, so the max of the
         // scores is the score of the max.
         float tmax = mx_keep;
-        int tanh_path = 2;  // 0: x*(1 - x^2/3), 1: degree-7 polynomial, 2: MUFU tanh
+        unsigned flags = 0;  // bit 0: |x| > poly-1 limit, bit 1: |x| > poly-3 limit, bit 2: rescale
         if constexpr (MODE == kModeSoftcap) {
           tmax = (mx_keep == -INFINITY) ? -INFINITY : tanh_approx(mx_keep * p.a);
           // Every |x| of the warp's rows decides (masked columns included: their raw scores
           // are ordinary finite numbers).
           const float mn_all = fminf(fminf(mna[0], mna[1]), fminf(mna[2], mna[3]));
           const float bound = fabsf(p.a) * fmaxf(fabsf(mx_all), fabsf(mn_all));
-          if (__all_sync(0xffffffffu, bound <= kTanhPoly1Limit)) tanh_path = 0;
-          else if (__all_sync(0xffffffffu, bound <= kTanhPoly3Limit)) tanh_path = 1;
+          flags = (bound > kTanhPoly1Limit ? 1u : 0u) | (bound > kTanhPoly3Limit ? 2u : 0u);
         }
         const float m_new = fmaxf(m_used, tmax * p.c2);
 
         // Lazy rescale: move the reference max only when it grew by more than 2^8.
         float alpha = 1.f;
-        bool need = false;
         if (m_new > -INFINITY && (m_used == -INFINITY || m_new - m_used > kRescaleThreshold)) {
-          need = true;
+          flags |= 4u;
           alpha = ex2_approx(m_used - m_new);  // 0 when m_used is -inf
           m_used = m_new;
         }
-        if (k > 0 && __any_sync(0xffffffffu, need)) {
+        flags = __reduce_or_sync(0xffffffffu, flags);  // one vote for all warp-level decisions
+        // 0: x*(1 - x^2/3), 1: degree-7 polynomial, 2: MUFU tanh
+        const int tanh_path = (flags & 2u) ? 2 : ((flags & 1u) ? 1 : 0);
+        if (k > 0 && (flags & 4u)) {
           // O_t must hold every PV up to k-1 and none may be in flight: PV(k-2) is known to be
           // complete (S(k) was computed after it), so pv_done is at most one phase behind.
           if (!mbar_wait(&bars->pv_done[t], (k - 1) & 1)) {
