@@ -296,6 +296,262 @@ __global__ void __launch_bounds__(kDecodeThreads)
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Grouped / paged decode on tensor cores (mma.sync m16n8k16, bf16 -> fp32).
+//
+// For G > 2 query rows per kv head (and for every paged cache) the FMA + shuffle form above
+// becomes instruction-bound long before HBM is saturated; here the G rows are the (zero-padded)
+// M dimension of 16x8x16 MMAs and the fragments come straight from 16-byte global loads:
+//
+//   QK^T  8 tokens at a time. Lane (n = lane/4, c = lane%4) loads the 16-byte pieces
+//         d = 32i + 8c .. +8 of token n's K row (i < D/32); the four 32-bit words of a piece
+//         are exactly the B fragments of two MMAs (a dot product does not care in which order
+//         the d's are visited as long as Q uses the same order, and Q is loaded with the same
+//         pattern, row g = lane/4 instead of token n).
+//   PV    16 tokens at a time. Lane (n, c) loads rows 2c, 2c+1, 2c+8, 2c+9 at d = 64h + 8n ..
+//         +8; a byte permute of two rows gives the {V[2c][d], V[2c+1][d]} pairs the B fragment
+//         wants; output column n of MMA (h, e) stands for d = 64h + 8n + e.
+//   The fp32 score fragment of the QK MMAs has the layout of the bf16 A fragment of the PV
+//   MMA, so P never leaves registers.
+// A CTA is one (batch, kv head, KV split); its 4 warps take alternate 16-token groups (one
+// page when page_size is 16) and are merged through shared memory like above.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_16816_rows0to7(float& d0, float& d1, uint32_t a0, uint32_t a2,
+                                                   uint32_t b0, uint32_t b1) {
+  float unused2, unused3;  // rows 8..15 of the tile are padding
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+      "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %10, %11};"
+      : "+f"(d0), "+f"(d1), "=f"(unused2), "=f"(unused3)
+      : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.f), "f"(0.f));
+}
+
+template <int D, bool PAGED, bool HAS_MOD>
+__global__ void __launch_bounds__(kDecodeThreads)
+    decode_mma_kernel(const DecodeParams p, const int G) {
+  constexpr int KI = D / 32;  // 16-byte pieces of a K row per lane
+  constexpr int VH = D / 64;  // 64-wide halves of a V row
+  constexpr int NT = D / 8;   // output n-tiles (8 columns each)
+
+  const int split = blockIdx.x;
+  const int kvh = blockIdx.y;
+  const int b = blockIdx.z;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2;  // query row of this lane's score / output fragment; token index n
+  const int c = lane & 3;
+
+  const int t0 = split * p.chunk;
+  const int t1 = min(p.Skv, t0 + p.chunk);
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  int32_t* s_pages_k = reinterpret_cast<int32_t*>(smem_raw);
+  int32_t* s_pages_v = s_pages_k;
+  int first_page = 0;
+  size_t merge_off = 0;
+  auto page_of = [&](int t) { return p.page_shift >= 0 ? (t >> p.page_shift) : (t / p.page_size); };
+  if constexpr (PAGED) {
+    int n_pages_local = 0;
+    if (t1 > t0) {
+      first_page = page_of(t0);
+      n_pages_local = page_of(t1 - 1) - first_page + 1;
+    }
+    const bool two_tables = p.block_table_v != p.block_table;
+    const int pages_pad = (n_pages_local + 3) & ~3;
+    if (two_tables) s_pages_v = s_pages_k + pages_pad;
+    merge_off = static_cast<size_t>(pages_pad) * 4 * (two_tables ? 2 : 1);
+    for (int which = 0; which < (two_tables ? 2 : 1); ++which) {
+      const int32_t* bt = (which == 0 ? p.block_table : p.block_table_v) +
+                          static_cast<int64_t>(b) * p.bt_stride + first_page;
+      int32_t* dst = which == 0 ? s_pages_k : s_pages_v;
+      for (int i = threadIdx.x; i < n_pages_local; i += kDecodeThreads) {
+        int32_t pg = bt[i];
+        if (pg < 0 || pg >= p.n_pages) {
+          if (p.status) atomicExch(p.status, LF_DEV_BAD_PAGE);
+          pg = 0;
+        }
+        dst[i] = pg;
+      }
+    }
+    __syncthreads();
+  }
+  float* s_merge = reinterpret_cast<float*>(smem_raw + merge_off);
+
+  // Row pointers of token t for this lane's kv head.
+  const __nv_bfloat16* kbase;
+  const __nv_bfloat16* vbase;
+  if constexpr (PAGED) {
+    kbase = p.k + kvh * p.k_stride[2];
+    vbase = p.v + kvh * p.v_stride[2];
+  } else {
+    kbase = p.k + b * p.k_stride[0] + kvh * p.k_stride[1];
+    vbase = p.v + b * p.v_stride[0] + kvh * p.v_stride[1];
+  }
+  auto k_row = [&](int t) -> const __nv_bfloat16* {
+    if constexpr (PAGED) {
+      const int pg_abs = page_of(t);
+      const int slot = t - pg_abs * p.page_size;
+      return kbase + static_cast<int64_t>(s_pages_k[pg_abs - first_page]) * p.k_stride[0] +
+             slot * p.k_stride[1];
+    } else {
+      return kbase + t * p.k_stride[2];
+    }
+  };
+  auto v_row = [&](int t) -> const __nv_bfloat16* {
+    if constexpr (PAGED) {
+      const int pg_abs = page_of(t);
+      const int slot = t - pg_abs * p.page_size;
+      return vbase + static_cast<int64_t>(s_pages_v[pg_abs - first_page]) * p.v_stride[0] +
+             slot * p.v_stride[1];
+    } else {
+      return vbase + t * p.v_stride[2];
+    }
+  };
+
+  // Q fragments (rows g >= G are zero padding).
+  uint4 qr[KI];
+#pragma unroll
+  for (int i = 0; i < KI; ++i) {
+    qr[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (g < G)
+      qr[i] = *reinterpret_cast<const uint4*>(p.q + b * p.q_stride[0] + kvh * p.q_stride[1] +
+                                              g * p.q_stride[2] + 32 * i + 8 * c);
+  }
+  const float smul = HAS_MOD ? p.scale : p.scale * kLog2e;
+
+  float m_run = -INFINITY, l_run = 0.f;
+  float o[NT][2];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) o[j][0] = o[j][1] = 0.f;
+
+  for (int tg = t0 + warp * 16; tg < t1; tg += 16 * kDecodeWarps) {
+    const int t_last = t1 - 1;
+    // K: token n = g of each 8-token half; V: rows 2c, 2c+1, 2c+8, 2c+9 of the 16-token group.
+    uint4 kr[2][KI], vr[VH][4];
+#pragma unroll
+    for (int s8 = 0; s8 < 2; ++s8) {
+      const __nv_bfloat16* row = k_row(min(tg + 8 * s8 + g, t_last)) + 8 * c;
+#pragma unroll
+      for (int i = 0; i < KI; ++i) kr[s8][i] = ldg_stream_16(row + 32 * i);
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int tok = tg + 2 * c + (r & 1) + 8 * (r >> 1);
+      const __nv_bfloat16* row = v_row(min(tok, t_last)) + 8 * g;
+#pragma unroll
+      for (int h = 0; h < VH; ++h) vr[h][r] = ldg_stream_16(row + 64 * h);
+    }
+
+    // Scores of the two 8-token halves: this lane ends up with tokens 2c, 2c+1 of each.
+    float sc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+#pragma unroll
+    for (int s8 = 0; s8 < 2; ++s8)
+#pragma unroll
+      for (int i = 0; i < KI; ++i) {
+        mma_16816_rows0to7(sc[s8][0], sc[s8][1], qr[i].x, qr[i].y, kr[s8][i].x, kr[s8][i].y);
+        mma_16816_rows0to7(sc[s8][0], sc[s8][1], qr[i].z, qr[i].w, kr[s8][i].z, kr[s8][i].w);
+      }
+    float mx = -INFINITY;
+#pragma unroll
+    for (int s8 = 0; s8 < 2; ++s8)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float v = sc[s8][e] * smul;
+        if constexpr (HAS_MOD) v = apply_mods(p.mods, v) * kLog2e;
+        if (tg + 8 * s8 + 2 * c + e >= t1) v = -INFINITY;
+        sc[s8][e] = v;
+        mx = fmaxf(mx, v);
+      }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);
+    const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+    const float alpha = ex2_approx(m_run - m_safe);
+    m_run = m_new;
+    float pr[2][2];
+    float psum = 0.f;
+#pragma unroll
+    for (int s8 = 0; s8 < 2; ++s8)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        pr[s8][e] = ex2_approx(sc[s8][e] - m_safe);
+        psum += pr[s8][e];
+      }
+    l_run = l_run * alpha + psum;  // this lane's share; the quad is summed after the loop
+    const uint32_t pa0 = pack_bf16x2(pr[0][0], pr[0][1]);
+    const uint32_t pa2 = pack_bf16x2(pr[1][0], pr[1][1]);
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      o[j][0] *= alpha;
+      o[j][1] *= alpha;
+    }
+#pragma unroll
+    for (int h = 0; h < VH; ++h) {
+      const uint32_t w0[4] = {vr[h][0].x, vr[h][0].y, vr[h][0].z, vr[h][0].w};
+      const uint32_t w1[4] = {vr[h][1].x, vr[h][1].y, vr[h][1].z, vr[h][1].w};
+      const uint32_t w2[4] = {vr[h][2].x, vr[h][2].y, vr[h][2].z, vr[h][2].w};
+      const uint32_t w3[4] = {vr[h][3].x, vr[h][3].y, vr[h][3].z, vr[h][3].w};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;  // high or low halves of two words
+        const uint32_t b0 = __byte_perm(w0[e >> 1], w1[e >> 1], sel);
+        const uint32_t b1 = __byte_perm(w2[e >> 1], w3[e >> 1], sel);
+        mma_16816_rows0to7(o[h * 8 + e][0], o[h * 8 + e][1], pa0, pa2, b0, b1);
+      }
+    }
+  }
+
+  // Row sum over the quad (the four lanes of a row hold disjoint tokens).
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+
+  // Merge the warps through shared memory: s_merge[warp][g][0..D) acc, then m, l.
+  constexpr int kStride = D + 2;
+  if (g < G) {
+    float* dst = s_merge + (warp * G + g) * kStride;
+#pragma unroll
+    for (int h = 0; h < VH; ++h)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        dst[64 * h + 16 * c + e] = o[h * 8 + e][0];      // output column 2c   -> d = 64h+16c+e
+        dst[64 * h + 16 * c + 8 + e] = o[h * 8 + e][1];  // output column 2c+1 -> d + 8
+      }
+    if (c == 0) {
+      dst[D] = m_run;
+      dst[D + 1] = l_run;
+    }
+  }
+  __syncthreads();
+
+  for (int idx = threadIdx.x; idx < G * D; idx += kDecodeThreads) {
+    const int gg = idx / D;
+    const int cc = idx - gg * D;
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w)
+      m_all = fmaxf(m_all, s_merge[(w * G + gg) * kStride + D]);
+    const float m_safe = (m_all == -INFINITY) ? 0.f : m_all;
+    float l_all = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w) {
+      const float* src = s_merge + (w * G + gg) * kStride;
+      const float a = ex2_approx(src[D] - m_safe);
+      l_all += src[D + 1] * a;
+      acc += src[cc] * a;
+    }
+    const int64_t unit = (static_cast<int64_t>(b) * p.Hkv + kvh) * G + gg;
+    if (p.splits == 1) {
+      __nv_bfloat16* op = p.out + b * p.o_stride[0] + kvh * p.o_stride[1] + gg * p.o_stride[2];
+      op[cc] = __float2bfloat16_rn(acc / l_all);
+    } else {
+      p.part_o[(unit * p.splits + split) * D + cc] = acc;
+      if (cc == 0) {
+        p.part_ml[(unit * p.splits + split) * 2] = m_all;
+        p.part_ml[(unit * p.splits + split) * 2 + 1] = l_all;
+      }
+    }
+  }
+}
+
 // Log-sum-exp combine of split-KV partials: one warp per (batch, kv head, g) output row.
 template <int D>
 __global__ void __launch_bounds__(128)
@@ -411,12 +667,23 @@ static int launch_decode_g(const DecodeParams& p, cudaStream_t st, size_t smem) 
 }
 
 template <int D, bool PAGED>
+static int launch_decode_mma(const DecodeParams& p, int G, cudaStream_t st, size_t smem) {
+  dim3 grid(p.splits, p.Hkv, p.B);
+  if (p.mods.n > 0)
+    decode_mma_kernel<D, PAGED, true><<<grid, kDecodeThreads, smem, st>>>(p, G);
+  else
+    decode_mma_kernel<D, PAGED, false><<<grid, kDecodeThreads, smem, st>>>(p, G);
+  return check_launch("decode_mma_kernel");
+}
+
+// Dense caches with one or two query rows per kv head stay on the FMA kernel (it already
+// streams at HBM speed there); everything else runs on the tensor-core kernel.
+template <int D, bool PAGED>
 static int launch_decode(const DecodeParams& p, int G, cudaStream_t st, size_t smem) {
+  if (PAGED || G > 2) return launch_decode_mma<D, PAGED>(p, G, st, smem);
   switch (G) {
     case 1: return launch_decode_g<D, 1, PAGED>(p, st, smem);
     case 2: return launch_decode_g<D, 2, PAGED>(p, st, smem);
-    case 4: return launch_decode_g<D, 4, PAGED>(p, st, smem);
-    case 8: return launch_decode_g<D, 8, PAGED>(p, st, smem);
     default: return LF_ERR_UNSUPPORTED;
   }
 }
