@@ -119,7 +119,7 @@ typedef struct {
   int32_t page_size;
   int32_t n_pages;
   /* split-KV */
-  int32_t splits;               /* >= 1; 0 = let the library choose */
+  int32_t splits;               /* 1..32; 0 = let the library choose */
   void* workspace;              /* device, >= lf_decode_workspace_bytes(...) when splits != 1 */
   size_t workspace_bytes;
   int32_t* status;              /* optional device word */

@@ -326,7 +326,7 @@ __device__ __forceinline__ void mma_16816_rows0to7(float& d0, float& d1, uint32_
 }
 
 template <int D, bool PAGED, bool HAS_MOD>
-__global__ void __launch_bounds__(kDecodeThreads)
+__global__ void __launch_bounds__(kDecodeThreads, 3)
     decode_mma_kernel(const DecodeParams p, const int G) {
   constexpr int KI = D / 32;  // 16-byte pieces of a K row per lane
   constexpr int VH = D / 64;  // 64-wide halves of a V row
@@ -423,16 +423,20 @@ __global__ void __launch_bounds__(kDecodeThreads)
 #pragma unroll
   for (int j = 0; j < NT; ++j) o[j][0] = o[j][1] = 0.f;
 
-  for (int tg = t0 + warp * 16; tg < t1; tg += 16 * kDecodeWarps) {
-    const int t_last = t1 - 1;
-    // K: token n = g of each 8-token half; V: rows 2c, 2c+1, 2c+8, 2c+9 of the 16-token group.
-    uint4 kr[2][KI], vr[VH][4];
+  // Loads run one 16-token group ahead of the arithmetic: K of the next group is requested as
+  // soon as QK^T has consumed the current K registers, V of the next group as soon as PV has
+  // consumed the current V registers, so every warp always has rows in flight.
+  const int t_last = t1 - 1;
+  uint4 kr[2][KI], vr[VH][4];
+  auto load_k = [&](int tg) {
 #pragma unroll
     for (int s8 = 0; s8 < 2; ++s8) {
       const __nv_bfloat16* row = k_row(min(tg + 8 * s8 + g, t_last)) + 8 * c;
 #pragma unroll
       for (int i = 0; i < KI; ++i) kr[s8][i] = ldg_stream_16(row + 32 * i);
     }
+  };
+  auto load_v = [&](int tg) {
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
       const int tok = tg + 2 * c + (r & 1) + 8 * (r >> 1);
@@ -440,6 +444,14 @@ __global__ void __launch_bounds__(kDecodeThreads)
 #pragma unroll
       for (int h = 0; h < VH; ++h) vr[h][r] = ldg_stream_16(row + 64 * h);
     }
+  };
+  if (t0 + warp * 16 < t1) {
+    load_k(t0 + warp * 16);
+    load_v(t0 + warp * 16);
+  }
+  for (int tg = t0 + warp * 16; tg < t1; tg += 16 * kDecodeWarps) {
+    const int tg_next = tg + 16 * kDecodeWarps;
+    // K: token n = g of each 8-token half; V: rows 2c, 2c+1, 2c+8, 2c+9 of the 16-token group.
 
     // Scores of the two 8-token halves: this lane ends up with tokens 2c, 2c+1 of each.
     float sc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
@@ -450,6 +462,7 @@ __global__ void __launch_bounds__(kDecodeThreads)
         mma_16816_rows0to7(sc[s8][0], sc[s8][1], qr[i].x, qr[i].y, kr[s8][i].x, kr[s8][i].y);
         mma_16816_rows0to7(sc[s8][0], sc[s8][1], qr[i].z, qr[i].w, kr[s8][i].z, kr[s8][i].w);
       }
+    if (tg_next < t1) load_k(tg_next);
     float mx = -INFINITY;
 #pragma unroll
     for (int s8 = 0; s8 < 2; ++s8)
@@ -498,6 +511,7 @@ __global__ void __launch_bounds__(kDecodeThreads)
         mma_16816_rows0to7(o[h * 8 + e][0], o[h * 8 + e][1], pa0, pa2, b0, b1);
       }
     }
+    if (tg_next < t1) load_v(tg_next);
   }
 
   // Row sum over the quad (the four lanes of a row hold disjoint tokens).
@@ -562,24 +576,46 @@ __global__ void __launch_bounds__(128)
   const int64_t unit = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (unit >= units) return;
+  // Lane s owns split s (at most 32 splits): one load round for all (max, sum) pairs, the
+  // weights are then broadcast from their lanes while the partial rows stream in.
   const float* ml = part_ml + unit * splits * 2;
-  float m_all = -INFINITY;
-  for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, ml[2 * s]);
+  float m_s = -INFINITY, l_s = 0.f;
+  if (lane < splits) {
+    const float2 v = *reinterpret_cast<const float2*>(ml + 2 * lane);
+    m_s = v.x;
+    l_s = v.y;
+  }
+  float m_all = m_s;
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1)
+    m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, off));
   const float m_safe = (m_all == -INFINITY) ? 0.f : m_all;
-  float l_all = 0.f;
+  const float w_s = ex2_approx(m_s - m_safe);
+  float l_all = l_s * w_s;
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) l_all += __shfl_xor_sync(0xffffffffu, l_all, off);
   float o[EPL];
 #pragma unroll
   for (int e = 0; e < EPL; ++e) o[e] = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float a = ex2_approx(ml[2 * s] - m_safe);
-    l_all += ml[2 * s + 1] * a;
-    const float* src = part_o + (unit * splits + s) * D + lane * EPL;
-    if constexpr (EPL == 4) {
-      const float4 x = *reinterpret_cast<const float4*>(src);
-      o[0] += x.x * a; o[1] += x.y * a; o[2] += x.z * a; o[3] += x.w * a;
-    } else {
-      const float2 x = *reinterpret_cast<const float2*>(src);
-      o[0] += x.x * a; o[1] += x.y * a;
+  const float* src0 = part_o + unit * splits * D + lane * EPL;
+  for (int s0 = 0; s0 < splits; s0 += 4) {
+    float x[4][EPL];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int s = min(s0 + u, splits - 1);
+      if constexpr (EPL == 4) {
+        const float4 v = *reinterpret_cast<const float4*>(src0 + s * D);
+        x[u][0] = v.x; x[u][1] = v.y; x[u][2] = v.z; x[u][3] = v.w;
+      } else {
+        const float2 v = *reinterpret_cast<const float2*>(src0 + s * D);
+        x[u][0] = v.x; x[u][1] = v.y;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float a = (s0 + u < splits) ? __shfl_sync(0xffffffffu, w_s, (s0 + u) & 31) : 0.f;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) o[e] += x[u][e] * a;
     }
   }
   const float inv = 1.f / l_all;
@@ -709,6 +745,7 @@ static int decode_impl(const LfDecodeArgs* a, void* stream, bool paged) {
   }
   int splits = a->splits;
   if (splits < 0) return LF_ERR_INVALID_ARG;
+  if (splits > 32) return LF_ERR_TOO_LARGE;
   if (splits == 0) splits = choose_splits(a->B, a->Hkv, a->G, a->Skv, a->D);
   // Token chunk per split: a multiple of 64 (and of the page size when that is a power of
   // two up to 64), so a split never starts in the middle of a warp's token batch.
@@ -804,6 +841,7 @@ int lf_combine_f32(const float* part_o, const float* part_ml, void* out, int32_t
   if (!part_o || !part_ml || !out || !o_stride) return LF_ERR_INVALID_ARG;
   if (B <= 0 || Hkv <= 0 || G <= 0 || splits <= 0) return LF_ERR_INVALID_ARG;
   if (D != 64 && D != 128) return LF_ERR_UNSUPPORTED;
+  if (splits > 32) return LF_ERR_TOO_LARGE;  // one lane per split in the combine
   const int64_t units = static_cast<int64_t>(B) * Hkv * G;
   const unsigned blocks = static_cast<unsigned>((units + 3) / 4);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
