@@ -153,7 +153,8 @@ void lf_skip_range(int32_t mask_kind, int32_t window, int32_t causal_offset, int
 int lf_decode_bf16(const LfDecodeArgs* args, void* stream);
 int lf_decode_paged_bf16(const LfDecodeArgs* args, void* stream);
 /* Split count the library picks for splits == 0, and the workspace it then needs. */
-int lf_decode_auto_splits(int32_t B, int32_t Hkv, int32_t G, int32_t Skv, int32_t D);
+int lf_decode_auto_splits(int32_t B, int32_t Hkv, int32_t G, int32_t Skv, int32_t D,
+                          int32_t paged);
 size_t lf_decode_workspace_bytes(int32_t B, int32_t Hkv, int32_t G, int32_t D, int32_t splits);
 
 /* Decode for callers that cannot allocate. No counterpart in the reference (it has neither

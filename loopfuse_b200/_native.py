@@ -87,7 +87,7 @@ def load() -> C.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = [C.POINTER(LfDecodeArgs), C.c_void_p]
         fn.restype = C.c_int
-    lib.lf_decode_auto_splits.argtypes = [C.c_int32] * 5
+    lib.lf_decode_auto_splits.argtypes = [C.c_int32] * 6
     lib.lf_decode_auto_splits.restype = C.c_int
     lib.lf_decode_workspace_bytes.argtypes = [C.c_int32] * 5
     lib.lf_decode_workspace_bytes.restype = C.c_size_t

@@ -62,6 +62,19 @@ __device__ __forceinline__ uint4 ldg_stream_16(const void* p) {
   return r;
 }
 
+// 16-byte asynchronous copy global -> shared (bypasses L1), grouped per thread.
+__device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // Three-input max / min (one instruction on sm_100).
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;

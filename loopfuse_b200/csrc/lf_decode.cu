@@ -25,6 +25,7 @@ constexpr int kDecodeWarps = 4;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
 constexpr int kDecodeUnroll = 4;
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kMmaStages = 3;  // cp.async ring depth of the tensor-core decode kernel
 
 struct DecodeParams {
   const __nv_bfloat16* q;
@@ -423,35 +424,71 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
 #pragma unroll
   for (int j = 0; j < NT; ++j) o[j][0] = o[j][1] = 0.f;
 
-  // Loads run one 16-token group ahead of the arithmetic: K of the next group is requested as
-  // soon as QK^T has consumed the current K registers, V of the next group as soon as PV has
-  // consumed the current V registers, so every warp always has rows in flight.
+  // K/V rows travel global -> shared with 16-byte cp.async into a ring private to the warp
+  // (kMmaStages groups of 16 tokens; kMmaStages-1 groups are in flight while one is consumed),
+  // so the bytes in flight do not cost registers. A 16-byte chunk j of row r sits at chunk
+  // position j ^ (r & 7): fragment reads of eight different rows then hit distinct banks.
+  constexpr int CPR = D / 8;               // 16-byte chunks per row
+  constexpr int kRowBytes = D * 2;
+  constexpr int kStageBytes = 2 * 16 * kRowBytes;  // 16 K rows then 16 V rows
   const int t_last = t1 - 1;
-  uint4 kr[2][KI], vr[VH][4];
-  auto load_k = [&](int tg) {
+  unsigned char* ring = smem_raw + merge_off + warp * (kMmaStages * kStageBytes);
+  const uint32_t ring_u32 = smem_u32(ring);
+  auto copy_group = [&](int tg, int stage) {
+    if (tg < t1) {
+      const uint32_t dst0 = ring_u32 + stage * kStageBytes;
+      const int j = lane % CPR;
+      const int r_max = t_last - tg;  // rows past the end of the split re-read the last token
+      // A group that lies inside one page (always true for dense caches) has affine row
+      // addresses: one table lookup per group instead of one per row.
+      bool one_page = true;
+      if constexpr (PAGED) one_page = page_of(tg) == page_of(min(tg + 15, t_last));
+      if (one_page) {
+        const __nv_bfloat16* kp = k_row(tg) + 8 * j;
+        const __nv_bfloat16* vp = v_row(tg) + 8 * j;
+        const int64_t ks = PAGED ? p.k_stride[1] : p.k_stride[2];
+        const int64_t vs = PAGED ? p.v_stride[1] : p.v_stride[2];
+#pragma unroll
+        for (int q = 0; q < 16 * CPR / 32; ++q) {
+          const int r = lane / CPR + q * (32 / CPR);
+          const int rc = min(r, r_max);
+          const uint32_t off = r * kRowBytes + ((j ^ (r & 7)) << 4);
+          cp_async_16(dst0 + off, kp + rc * ks);
+          cp_async_16(dst0 + 16 * kRowBytes + off, vp + rc * vs);
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 16 * CPR / 32; ++q) {
+          const int r = lane / CPR + q * (32 / CPR);
+          const int tok = tg + min(r, r_max);
+          const uint32_t off = r * kRowBytes + ((j ^ (r & 7)) << 4);
+          cp_async_16(dst0 + off, k_row(tok) + 8 * j);
+          cp_async_16(dst0 + 16 * kRowBytes + off, v_row(tok) + 8 * j);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+  const int tg0 = t0 + warp * 16;
+#pragma unroll
+  for (int st = 0; st < kMmaStages - 1; ++st) copy_group(tg0 + st * 16 * kDecodeWarps, st);
+
+  int it = 0;
+  for (int tg = tg0; tg < t1; tg += 16 * kDecodeWarps, ++it) {
+    copy_group(tg + (kMmaStages - 1) * 16 * kDecodeWarps, (it + kMmaStages - 1) % kMmaStages);
+    cp_async_wait<kMmaStages - 1>();
+    __syncwarp();
+    const unsigned char* stage = ring + (it % kMmaStages) * kStageBytes;
+    // K: token n = g of each 8-token half; V: rows 2c, 2c+1, 2c+8, 2c+9 of the 16-token group.
+    uint4 kr[2][KI];
 #pragma unroll
     for (int s8 = 0; s8 < 2; ++s8) {
-      const __nv_bfloat16* row = k_row(min(tg + 8 * s8 + g, t_last)) + 8 * c;
+      const int r = 8 * s8 + g;
 #pragma unroll
-      for (int i = 0; i < KI; ++i) kr[s8][i] = ldg_stream_16(row + 32 * i);
+      for (int i = 0; i < KI; ++i)
+        kr[s8][i] = *reinterpret_cast<const uint4*>(stage + r * kRowBytes +
+                                                    (((4 * i + c) ^ (r & 7)) << 4));
     }
-  };
-  auto load_v = [&](int tg) {
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int tok = tg + 2 * c + (r & 1) + 8 * (r >> 1);
-      const __nv_bfloat16* row = v_row(min(tok, t_last)) + 8 * g;
-#pragma unroll
-      for (int h = 0; h < VH; ++h) vr[h][r] = ldg_stream_16(row + 64 * h);
-    }
-  };
-  if (t0 + warp * 16 < t1) {
-    load_k(t0 + warp * 16);
-    load_v(t0 + warp * 16);
-  }
-  for (int tg = t0 + warp * 16; tg < t1; tg += 16 * kDecodeWarps) {
-    const int tg_next = tg + 16 * kDecodeWarps;
-    // K: token n = g of each 8-token half; V: rows 2c, 2c+1, 2c+8, 2c+9 of the 16-token group.
 
     // Scores of the two 8-token halves: this lane ends up with tokens 2c, 2c+1 of each.
     float sc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
@@ -462,7 +499,6 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
         mma_16816_rows0to7(sc[s8][0], sc[s8][1], qr[i].x, qr[i].y, kr[s8][i].x, kr[s8][i].y);
         mma_16816_rows0to7(sc[s8][0], sc[s8][1], qr[i].z, qr[i].w, kr[s8][i].z, kr[s8][i].w);
       }
-    if (tg_next < t1) load_k(tg_next);
     float mx = -INFINITY;
 #pragma unroll
     for (int s8 = 0; s8 < 2; ++s8)
@@ -499,10 +535,17 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
     }
 #pragma unroll
     for (int h = 0; h < VH; ++h) {
-      const uint32_t w0[4] = {vr[h][0].x, vr[h][0].y, vr[h][0].z, vr[h][0].w};
-      const uint32_t w1[4] = {vr[h][1].x, vr[h][1].y, vr[h][1].z, vr[h][1].w};
-      const uint32_t w2[4] = {vr[h][2].x, vr[h][2].y, vr[h][2].z, vr[h][2].w};
-      const uint32_t w3[4] = {vr[h][3].x, vr[h][3].y, vr[h][3].z, vr[h][3].w};
+      uint4 vq[4];
+#pragma unroll
+      for (int r4 = 0; r4 < 4; ++r4) {
+        const int r = 2 * c + (r4 & 1) + 8 * (r4 >> 1);
+        vq[r4] = *reinterpret_cast<const uint4*>(stage + (16 + r) * kRowBytes +
+                                                 (((8 * h + g) ^ (r & 7)) << 4));
+      }
+      const uint32_t w0[4] = {vq[0].x, vq[0].y, vq[0].z, vq[0].w};
+      const uint32_t w1[4] = {vq[1].x, vq[1].y, vq[1].z, vq[1].w};
+      const uint32_t w2[4] = {vq[2].x, vq[2].y, vq[2].z, vq[2].w};
+      const uint32_t w3[4] = {vq[3].x, vq[3].y, vq[3].z, vq[3].w};
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;  // high or low halves of two words
@@ -511,15 +554,18 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
         mma_16816_rows0to7(o[h * 8 + e][0], o[h * 8 + e][1], pa0, pa2, b0, b1);
       }
     }
-    if (tg_next < t1) load_v(tg_next);
+    __syncwarp();  // every lane is done with this stage before it is refilled
   }
+  cp_async_wait<0>();
 
   // Row sum over the quad (the four lanes of a row hold disjoint tokens).
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
 
-  // Merge the warps through shared memory: s_merge[warp][g][0..D) acc, then m, l.
+  // Merge the warps through shared memory: s_merge[warp][g][0..D) acc, then m, l. The merge
+  // area reuses the rings, so every warp must have finished reading its last stage.
   constexpr int kStride = D + 2;
+  __syncthreads();
   if (g < G) {
     float* dst = s_merge + (warp * G + g) * kStride;
 #pragma unroll
@@ -676,17 +722,26 @@ static int device_sm_count() {
 
 static int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
-static int choose_splits(int B, int Hkv, int G, int Skv, int D) {
-  (void)G;
+static bool uses_mma_kernel(int G, bool paged) { return paged || G > 2; }
+
+static int choose_splits(int B, int Hkv, int G, int Skv, int D, bool paged) {
   (void)D;
   const int units = B * Hkv;
   const int sms = device_sm_count();
-  // Aim for >= 6 waves of 8 resident CTAs per SM so the tail wave is cheap, but keep at
-  // least 256 tokens per split so the per-CTA prologue/epilogue stays amortised.
-  const int want = (sms * 8 * 6 + units - 1) / units;
-  int max_by_len = Skv / 256;
+  int max_by_len = Skv / 256;  // keep >= 256 tokens per split
   if (max_by_len < 1) max_by_len = 1;
-  int s = want < max_by_len ? want : max_by_len;
+  int s;
+  if (uses_mma_kernel(G, paged)) {
+    // Two CTAs of the tensor-core kernel are resident per SM and each keeps ~16 KB in flight
+    // per warp, so one wave already saturates HBM: split only to fill the machine (splitting
+    // costs the partial round trip and a short, badly pipelined loop per CTA).
+    const int resident = sms * 2;
+    s = units >= resident ? 1 : (resident + units - 1) / units;
+  } else {
+    // The FMA kernel has ~8 small CTAs per SM: aim for >= 6 waves so the tail wave is cheap.
+    s = (sms * 8 * 6 + units - 1) / units;
+  }
+  if (s > max_by_len) s = max_by_len;
   if (s < 1) s = 1;
   if (s > 32) s = 32;
   return s;
@@ -705,6 +760,26 @@ static int launch_decode_g(const DecodeParams& p, cudaStream_t st, size_t smem) 
 template <int D, bool PAGED>
 static int launch_decode_mma(const DecodeParams& p, int G, cudaStream_t st, size_t smem) {
   dim3 grid(p.splits, p.Hkv, p.B);
+  // page ids + the per-warp K/V rings (the warp-merge area reuses the rings)
+  const size_t ring = static_cast<size_t>(kDecodeWarps) * kMmaStages * 2 * 16 * D * 2;
+  const size_t merge = static_cast<size_t>(kDecodeWarps) * G * (D + 2) * sizeof(float);
+  smem = smem - merge + (ring > merge ? ring : merge);
+  static thread_local int configured_dev[2] = {-1, -1};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_dev[p.mods.n > 0] != dev) {
+    cudaError_t e =
+        p.mods.n > 0
+            ? cudaFuncSetAttribute(decode_mma_kernel<D, PAGED, true>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024)
+            : cudaFuncSetAttribute(decode_mma_kernel<D, PAGED, false>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    if (e != cudaSuccess) {
+      set_cuda_error(e, "cudaFuncSetAttribute(decode_mma_kernel)");
+      return LF_ERR_CUDA;
+    }
+    configured_dev[p.mods.n > 0] = dev;
+  }
   if (p.mods.n > 0)
     decode_mma_kernel<D, PAGED, true><<<grid, kDecodeThreads, smem, st>>>(p, G);
   else
@@ -716,7 +791,7 @@ static int launch_decode_mma(const DecodeParams& p, int G, cudaStream_t st, size
 // streams at HBM speed there); everything else runs on the tensor-core kernel.
 template <int D, bool PAGED>
 static int launch_decode(const DecodeParams& p, int G, cudaStream_t st, size_t smem) {
-  if (PAGED || G > 2) return launch_decode_mma<D, PAGED>(p, G, st, smem);
+  if (uses_mma_kernel(G, PAGED)) return launch_decode_mma<D, PAGED>(p, G, st, smem);
   switch (G) {
     case 1: return launch_decode_g<D, 1, PAGED>(p, st, smem);
     case 2: return launch_decode_g<D, 2, PAGED>(p, st, smem);
@@ -746,7 +821,7 @@ static int decode_impl(const LfDecodeArgs* a, void* stream, bool paged) {
   int splits = a->splits;
   if (splits < 0) return LF_ERR_INVALID_ARG;
   if (splits > 32) return LF_ERR_TOO_LARGE;
-  if (splits == 0) splits = choose_splits(a->B, a->Hkv, a->G, a->Skv, a->D);
+  if (splits == 0) splits = choose_splits(a->B, a->Hkv, a->G, a->Skv, a->D, paged);
   // Token chunk per split: a multiple of 64 (and of the page size when that is a power of
   // two up to 64), so a split never starts in the middle of a warp's token batch.
   int chunk = round_up((a->Skv + splits - 1) / splits, 64);
@@ -815,9 +890,10 @@ static int decode_impl(const LfDecodeArgs* a, void* stream, bool paged) {
 
 extern "C" {
 
-int lf_decode_auto_splits(int32_t B, int32_t Hkv, int32_t G, int32_t Skv, int32_t D) {
+int lf_decode_auto_splits(int32_t B, int32_t Hkv, int32_t G, int32_t Skv, int32_t D,
+                          int32_t paged) {
   if (B <= 0 || Hkv <= 0 || Skv <= 0) return 1;
-  int splits = lf::choose_splits(B, Hkv, G, Skv, D);
+  int splits = lf::choose_splits(B, Hkv, G, Skv, D, paged != 0);
   const int chunk = lf::round_up((Skv + splits - 1) / splits, 64);
   return (Skv + chunk - 1) / chunk;
 }
@@ -940,7 +1016,8 @@ extern "C" int lf_decode_bf16_static(const LfDecodeArgs* args, void* stream) {
   // Resolve the split count exactly as lf_decode_bf16 will, then size the partials.
   int splits = args->splits;
   if (splits < 0) return LF_ERR_INVALID_ARG;
-  if (splits == 0) splits = lf::choose_splits(args->B, args->Hkv, args->G, args->Skv, args->D);
+  if (splits == 0)
+    splits = lf::choose_splits(args->B, args->Hkv, args->G, args->Skv, args->D, false);
   const int chunk = lf::round_up((args->Skv + splits - 1) / splits, 64);
   splits = (args->Skv + chunk - 1) / chunk;
   const size_t need = lf_decode_workspace_bytes(args->B, args->Hkv, args->G, args->D, splits);

@@ -129,7 +129,8 @@ class DecodeWorkspace:
 _default_ws = DecodeWorkspace()
 
 
-def _decode_common(q, out, B, Hkv, G, Skv, D, scale, mods, splits, workspace, status, dev):
+def _decode_common(q, out, B, Hkv, G, Skv, D, scale, mods, splits, workspace, status, dev,
+                   paged=False):
     a = _native.LfDecodeArgs()
     a.q, a.out = q.data_ptr(), out.data_ptr()
     a.B, a.Hkv, a.G, a.Skv, a.D = B, Hkv, G, Skv, D
@@ -139,7 +140,7 @@ def _decode_common(q, out, B, Hkv, G, Skv, D, scale, mods, splits, workspace, st
     _fill_mods(a, scale, mods)
     lib = _native.load()
     with torch.cuda.device(dev):
-        n_splits = splits if splits else lib.lf_decode_auto_splits(B, Hkv, G, Skv, D)
+        n_splits = splits if splits else lib.lf_decode_auto_splits(B, Hkv, G, Skv, D, int(paged))
     a.splits = n_splits
     nbytes = lib.lf_decode_workspace_bytes(B, Hkv, G, D, n_splits)
     ws = (workspace or _default_ws).get(nbytes, dev)
@@ -226,7 +227,8 @@ def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
         bt = bt.contiguous()
     if out is None:
         out = torch.empty((B, Hkv, G, D), dtype=torch.bfloat16, device=dev)
-    a, ws = _decode_common(q, out, B, Hkv, G, Skv, D, scale, mods, splits, workspace, status, dev)
+    a, ws = _decode_common(q, out, B, Hkv, G, Skv, D, scale, mods, splits, workspace, status, dev,
+                           paged=True)
     a.k, a.v = k_pool.data_ptr(), v_pool.data_ptr()
     for i in range(3):
         a.k_stride[i] = k_pool.stride(i)
