@@ -6,8 +6,8 @@
 //
 //   warps 0-3   softmax for query tile 0 (one thread per score row)
 //   warps 4-7   softmax for query tile 1
-//   warp  8     TMA producer: Q tiles once, then K/V tiles into a ring, in the order the MMA
-//               warp consumes them: K(lo), K(lo+1), V(lo), K(lo+2), V(lo+1), ...
+//   warp  8     TMA producer: Q tiles once, then pairs of K/V tiles into a ring, in the order
+//               the MMA warps consume them: {K(lo), K(lo+1)}, {V(lo), K(lo+2)}, {V(lo+1), ...
 //   warp  9/10  MMA issuers (one thread each, one per query tile): S_t[buf] = Q_t K^T,
 //               O_t += P_t V
 //
@@ -18,8 +18,8 @@
 // S is double-buffered per query tile: QK^T of KV tile j+2 is issued right after PV of tile j,
 // so the tensor pipe computes the next scores while the softmax warps work on the current
 // ones; the only dependency left between the two sides is "PV(j) needs P(j)". The softmax warps
-// rescale O_t in place when the running max moves by more than 2^8 (rare); for that they wait
-// on `pv_done`, which the MMA warp commits after every PV.
+// rescale O_t in place when the running max moves by more than 2^8 (rare); "S(k+1) is ready"
+// tells them that PV(k-1) is complete.
 //
 // Shared-memory tiles use the 128-byte swizzle that TMA writes and the MMA descriptors read:
 // a [rows][D] bf16 tile is stored as D/64 blocks of [rows][64] (128-byte rows).
@@ -41,11 +41,12 @@ constexpr int kTileK = LF_PREFILL_TILE_K;
 static_assert(kTileQ == 128 && kTileK == 64, "the kernel is written for 128 x 64 tiles");
 constexpr int kPrefillThreads = 352;
 constexpr int kMaxStages = 16;
-// K/V ring depth: 8 x 16 KB tiles at D=128, 16 x 8 KB at D=64 (which also keeps the CTA above
-// half of the shared memory, so two CTAs never compete for the 512 tensor-memory columns).
+// K/V ring depth in stages of two 64-key tiles: 4 x 32 KB at D=128, 8 x 16 KB at D=64 (which
+// also keeps the CTA above half of the shared memory, so two CTAs never compete for the 512
+// tensor-memory columns).
 template <int D>
 struct StagesFor {
-  static constexpr int value = D == 64 ? 16 : 8;
+  static constexpr int value = D == 64 ? 8 : 4;
 };
 constexpr float kLog2eF = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 domain
@@ -213,7 +214,10 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       }
       int n = 0;
       bool ok = true;
-      auto load = [&](const CUtensorMap* tm, int j) {
+      // A ring stage holds two 64-key tiles that the MMA warps need at the same time:
+      // {K(lo), K(lo+1)} first, then {V(j), K(j+2)} for every j; one full / one empty barrier
+      // per stage. `jb < 0` means the second half is not loaded (past the end of the range).
+      auto load_pair = [&](const CUtensorMap* tma, int ja, int jb) {
         if (!ok) return;
         const int stage = n % kStages;
         const uint32_t parity = ((n / kStages) & 1) ^ 1;
@@ -225,19 +229,22 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
           return;
         }
         LF_TRACE_EV(2);
-        mbar_arrive_expect_tx(&bars->kv_full[stage], kKVTileBytes);
+        mbar_arrive_expect_tx(&bars->kv_full[stage], jb >= 0 ? 2 * kKVTileBytes : kKVTileBytes);
+        unsigned char* dst = sKV + stage * (2 * kKVTileBytes);
 #pragma unroll
         for (int kb = 0; kb < kBlocksD; ++kb)
-          tma_load_4d(sKV + stage * kKVTileBytes + kb * kKVBlockBytes, tm, &bars->kv_full[stage],
-                      kb * 64, j * kTileK, hkv, b);
+          tma_load_4d(dst + kb * kKVBlockBytes, tma, &bars->kv_full[stage], kb * 64, ja * kTileK,
+                      hkv, b);
+        if (jb >= 0) {
+#pragma unroll
+          for (int kb = 0; kb < kBlocksD; ++kb)
+            tma_load_4d(dst + kKVTileBytes + kb * kKVBlockBytes, &tmap_k, &bars->kv_full[stage],
+                        kb * 64, jb * kTileK, hkv, b);
+        }
       };
       if (hi > lo) {
-        load(&tmap_k, lo);
-        if (lo + 1 < hi) load(&tmap_k, lo + 1);
-        for (int j = lo; j < hi; ++j) {
-          load(&tmap_v, j);
-          if (j + 2 < hi) load(&tmap_k, j + 2);
-        }
+        load_pair(&tmap_k, lo, lo + 1 < hi ? lo + 1 : -1);
+        for (int j = lo; j < hi; ++j) load_pair(&tmap_v, j, j + 2 < hi ? j + 2 : -1);
       }
       LF_TRACE_END();
     }
@@ -257,7 +264,8 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       }
       // Descriptors are built once; per MMA only the start-address field moves (in 16-byte
       // units, no carry out of the 14-bit field since shared memory ends below 256 KB).
-      constexpr uint32_t kStageUnits = kKVTileBytes >> 4;
+      constexpr uint32_t kStageUnits = (2 * kKVTileBytes) >> 4;  // a stage is a pair of tiles
+      constexpr uint32_t kHalfUnits = kKVTileBytes >> 4;
       const uint64_t qdesc = make_smem_desc_sw128(smem_u32(sQ) + t * kQTileBytes, 16, 1024);
       const uint64_t kdesc0 = make_smem_desc_sw128(smem_u32(sKV), 16, 1024);
       const uint64_t vdesc0 = make_smem_desc_sw128(smem_u32(sKV), kKVBlockBytes, 1024);
@@ -266,7 +274,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       int n = 0;  // ring position, walks the same sequence as the producer
 
       auto active = [&](int j) { return has_work[t] && j >= lo_t[t] && j < hi_t[t]; };
-      auto wait_slot = [&](int where) -> int {  // next ring slot, waited full; -1 on time-out
+      auto wait_stage = [&](int where) -> int {  // next ring stage, waited full; -1 on time-out
         const int stage = n % kStages;
         const uint32_t parity = (n / kStages) & 1;
         ++n;
@@ -277,9 +285,10 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         }
         return stage;
       };
-      auto issue_qk = [&](int stage, int j) {
+      // `half` selects the first or second tile of the stage.
+      auto issue_qk = [&](int stage, int half, int j) {
         const int buf = (j - lo_t[t]) & 1;
-        const uint64_t kd = kdesc0 + static_cast<uint64_t>(stage * kStageUnits);
+        const uint64_t kd = kdesc0 + static_cast<uint64_t>(stage * kStageUnits + half * kHalfUnits);
         const uint32_t d = s_col + buf * 64;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
@@ -297,27 +306,23 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
           mma_ts(o_col, a + ks * 8, vd + static_cast<uint64_t>(ks * (2048 >> 4)), kIdescPV,
                  (kt > 0 || ks > 0) ? 1u : 0u);
         }
-        tc_commit(&bars->pv_done[t]);
       };
 
-      // Prologue: scores of the first two KV tiles.
-      for (int jj = lo; jj < hi && jj < lo + 2 && ok; ++jj) {
-        const int stage = wait_slot(3);
-        if (stage < 0) break;
-        tc_fence_after();
-        if (active(jj)) issue_qk(stage, jj);
-        tc_commit(&bars->kv_empty[stage]);
+      // Prologue: scores of the first two KV tiles (one stage).
+      if (ok) {
+        const int stage = wait_stage(3);
+        if (stage >= 0) {
+          tc_fence_after();
+          if (active(lo)) issue_qk(stage, 0, lo);
+          if (lo + 1 < hi && active(lo + 1)) issue_qk(stage, 1, lo + 1);
+          tc_commit(&bars->kv_empty[stage]);
+        }
       }
+      const int nblk_t = has_work[t] ? hi_t[t] - lo_t[t] : 0;
       for (int j = lo; j < hi && ok; ++j) {
         LF_TRACE_EV(10);
-        const int sv = wait_slot(4);
-        if (sv < 0) break;
-        const bool k2 = j + 2 < hi;
-        int sk = 0;
-        if (k2) {
-          sk = wait_slot(5);
-          if (sk < 0) break;
-        }
+        const int st = wait_stage(4);  // {V(j), K(j+2)}
+        if (st < 0) break;
         tc_fence_after();
         LF_TRACE_EV(11);
         if (active(j)) {
@@ -329,15 +334,15 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
           }
           tc_fence_after();
           LF_TRACE_EV(13);
-          issue_pv(sv, kt);
+          issue_pv(st, kt);
           LF_TRACE_EV(14);
-          if (j == hi_t[t] - 1) tc_commit(&bars->o_final[t]);
+          // Completion points the softmax warps may wait on: the second-to-last PV (for a
+          // rescale in the last block) and the last PV (for the epilogue).
+          if (kt == nblk_t - 2) tc_commit(&bars->pv_done[t]);
+          if (kt == nblk_t - 1) tc_commit(&bars->o_final[t]);
         }
-        tc_commit(&bars->kv_empty[sv]);
-        if (k2) {
-          if (active(j + 2)) issue_qk(sk, j + 2);
-          tc_commit(&bars->kv_empty[sk]);
-        }
+        if (j + 2 < hi && active(j + 2)) issue_qk(st, 1, j + 2);
+        tc_commit(&bars->kv_empty[st]);
         LF_TRACE_EV(15);
       }
       LF_TRACE_END();
@@ -462,9 +467,12 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         // 0: x*(1 - x^2/3), 1: degree-7 polynomial, 2: MUFU tanh
         const int tanh_path = (flags & 2u) ? 2 : ((flags & 1u) ? 1 : 0);
         if (k > 0 && (flags & 4u)) {
-          // O_t must hold every PV up to k-1 and none may be in flight: PV(k-2) is known to be
-          // complete (S(k) was computed after it), so pv_done is at most one phase behind.
-          if (!mbar_wait(&bars->pv_done[t], (k - 1) & 1)) {
+          // O_t must hold every PV up to k-1 and none may be in flight. QK(k+1) is issued after
+          // PV(k-1), so "S(k+1) is ready" implies it; in the last block there is no S(k+1) and
+          // the MMA warp commits pv_done after the second-to-last PV instead.
+          const bool last = k + 1 == nblk;
+          uint64_t* bar = last ? &bars->pv_done[t] : &bars->s_full[t][(k + 1) & 1];
+          if (!mbar_wait(bar, last ? 0u : (((k + 1) >> 1) & 1))) {
             report_timeout(p.status, 12 + t);
             ok = false;
             break;
@@ -488,6 +496,15 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         const uint64_t neg_m2 = pack2(-m_safe, -m_safe);
         uint64_t psum2[4] = {0ull, 0ull, 0ull, 0ull};
         uint32_t pk[32];
+        // One pair in four takes its exponentials on the FMA pipe instead of MUFU (which is the
+        // busiest pipe of this loop): 2^z = 2^n * 2^f with n = round(z) taken from the low
+        // mantissa bits of z + 1.5*2^23, f = z - n in [-0.5, 0.5] and a cubic for 2^f (relative
+        // error 7.5e-5, far below the bf16 rounding of P); n is added into the exponent field.
+        const uint64_t magic2 = pack2(12582912.f, 12582912.f);
+        const uint64_t neg_magic2 = pack2(-12582912.f, -12582912.f);
+        const uint64_t minus_one2 = pack2(-1.f, -1.f);
+        const uint64_t e0 = pack2(0.99992811f, 0.99992811f), e1 = pack2(0.69326099f, 0.69326099f);
+        const uint64_t e2 = pack2(0.24261054f, 0.24261054f), e3 = pack2(0.05517132f, 0.05517132f);
         auto finish_pair = [&](uint64_t z2, int c, int i, bool apply_mask) {
           float z0, z1;
           unpack2(z2, z0, z1);
@@ -496,7 +513,23 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
             if (cc < rel_lo || cc > rel_hi) z0 = -INFINITY;
             if (cc + 1 < rel_lo || cc + 1 > rel_hi) z1 = -INFINITY;
           }
-          const float p0 = ex2_approx(z0), p1 = ex2_approx(z1);
+          float p0, p1;
+          if (((c * 16 + (i >> 1)) & 3) == 3) {
+            const uint64_t zc2 = pack2(fmaxf(z0, -120.f), fmaxf(z1, -120.f));
+            const uint64_t r2 = add2(zc2, magic2);
+            const uint64_t f2 = fma2(add2(r2, neg_magic2), minus_one2, zc2);
+            uint64_t q2 = fma2(f2, e3, e2);
+            q2 = fma2(q2, f2, e1);
+            q2 = fma2(q2, f2, e0);
+            float q0, q1, r0, r1;
+            unpack2(q2, q0, q1);
+            unpack2(r2, r0, r1);
+            p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23));
+            p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
+          } else {
+            p0 = ex2_approx(z0);
+            p1 = ex2_approx(z1);
+          }
           psum2[(c * 2 + (i >> 1)) & 3] = add2(psum2[(c * 2 + (i >> 1)) & 3], pack2(p0, p1));
           pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
         };
@@ -687,7 +720,7 @@ static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CU
   constexpr size_t kQTileBytes = static_cast<size_t>(kTileQ) * D * 2;
   constexpr size_t kKVTileBytes = static_cast<size_t>(kTileK) * D * 2;
   constexpr size_t smem = 1024 /*align slack*/ + 1024 /*barriers*/ + 2 * kQTileBytes +
-                          StagesFor<D>::value * kKVTileBytes;
+                          StagesFor<D>::value * 2 * kKVTileBytes;
   static thread_local int configured_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
