@@ -41,6 +41,7 @@ constexpr int kTileK = LF_PREFILL_TILE_K;
 static_assert(kTileQ == 128 && kTileK == 64, "the kernel is written for 128 x 64 tiles");
 constexpr int kPrefillThreads = 352;
 constexpr int kMaxStages = 16;
+constexpr uint32_t kStageBytesTotal = 8 * 2048;
 // K/V ring depth in stages of two 64-key tiles: 4 x 32 KB at D=128, 8 x 16 KB at D=64 (which
 // also keeps the CTA above half of the shared memory, so two CTAs never compete for the 512
 // tensor-memory columns).
@@ -136,7 +137,8 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~static_cast<uintptr_t>(1023));
   PrefillBarriers* bars = reinterpret_cast<PrefillBarriers*>(smem);
-  unsigned char* sQ = smem + 1024;
+  unsigned char* sStage = smem + 1024;  // 8 x 2 KB: output staging of the softmax warps
+  unsigned char* sQ = sStage + kStageBytesTotal;
   unsigned char* sKV = sQ + 2 * kQTileBytes;
 
   const int warp = threadIdx.x >> 5;
@@ -619,27 +621,42 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       if (ok) {
         tc_fence_after();
         const float inv = 1.f / l_run;
-        __nv_bfloat16* orow = p.out + b * p.o_stride[0] + h * p.o_stride[1] +
-                              static_cast<int64_t>(grow) * p.o_stride[2];
+        // Each warp owns 32 rows. A 32-column chunk (64 bytes per row) goes through a swizzled
+        // 2 KB buffer of the warp so that one store instruction writes eight 64-byte row
+        // segments instead of thirty-two 16-byte pieces.
+        unsigned char* stage = sStage + warp * 2048;
+        __nv_bfloat16* obase = p.out + b * p.o_stride[0] + h * p.o_stride[1];
+        const int row0 = (iq0 + t) * kTileQ + (warp & 3) * 32;  // first global row of the warp
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t orr[32];
           tmem_ld_32x32b_x32(o_addr + c * 32, orr);
           tmem_wait_ld();
-          if (grow < p.Sq) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 w;
-              w.x = pack_bf16x2(__uint_as_float(orr[i]) * inv, __uint_as_float(orr[i + 1]) * inv);
-              w.y = pack_bf16x2(__uint_as_float(orr[i + 2]) * inv,
-                                __uint_as_float(orr[i + 3]) * inv);
-              w.z = pack_bf16x2(__uint_as_float(orr[i + 4]) * inv,
-                                __uint_as_float(orr[i + 5]) * inv);
-              w.w = pack_bf16x2(__uint_as_float(orr[i + 6]) * inv,
-                                __uint_as_float(orr[i + 7]) * inv);
-              *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
-            }
+          for (int q = 0; q < 4; ++q) {  // piece q of row r sits at position q ^ ((r >> 1) & 3)
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(orr[8 * q]) * inv,
+                              __uint_as_float(orr[8 * q + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(orr[8 * q + 2]) * inv,
+                              __uint_as_float(orr[8 * q + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(orr[8 * q + 4]) * inv,
+                              __uint_as_float(orr[8 * q + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(orr[8 * q + 6]) * inv,
+                              __uint_as_float(orr[8 * q + 7]) * inv);
+            *reinterpret_cast<uint4*>(stage + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) = w;
           }
+          __syncwarp();
+#pragma unroll
+          for (int rr = 0; rr < 4; ++rr) {
+            const int r = rr * 8 + (lane >> 2);
+            const int q = lane & 3;
+            const uint4 w =
+                *reinterpret_cast<const uint4*>(stage + r * 64 + ((q ^ ((r >> 1) & 3)) << 4));
+            if (row0 + r < p.Sq)
+              *reinterpret_cast<uint4*>(obase + static_cast<int64_t>(row0 + r) * p.o_stride[2] +
+                                        c * 32 + q * 8) = w;
+          }
+          __syncwarp();
         }
       }
       LF_TRACE_EV(27);
@@ -719,7 +736,8 @@ static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CU
                           const PrefillParams& p, int B, cudaStream_t st) {
   constexpr size_t kQTileBytes = static_cast<size_t>(kTileQ) * D * 2;
   constexpr size_t kKVTileBytes = static_cast<size_t>(kTileK) * D * 2;
-  constexpr size_t smem = 1024 /*align slack*/ + 1024 /*barriers*/ + 2 * kQTileBytes +
+  constexpr size_t smem = 1024 /*align slack*/ + 1024 /*barriers*/ + kStageBytesTotal +
+                          2 * kQTileBytes +
                           StagesFor<D>::value * 2 * kKVTileBytes;
   static thread_local int configured_dev = -1;
   int dev = 0;
