@@ -36,6 +36,16 @@ sys.path.insert(0, str(ROOT))
 
 METRIC = "prefill TFLOP/s (causal-adjusted FLOPs) per job; decode HBM GB/s under `others`"
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one full-size launch of each
+# workload's dominant kernel, from the ncu captures summarised under profiles/: captured on a
+# smaller batch and scaled by the batch ratio (the traffic is proportional to the batch).
+NCU_TRAFFIC_BYTES = {
+    "causal_softcap": 4 * (100.78e6 + 15.63e6),
+    "window_gqa_softcap": 2 * (100.76e6 + 36.68e6),
+    "decode": 8 * (268.51e6 + 4.59e6),
+    "paged_decode_gqa": 2 * (268.79e6 + 4.74e6),
+}
+
 
 def load_peaks() -> tuple[dict, str]:
     path = ROOT / "MEASURED_PEAKS.json"
@@ -371,7 +381,7 @@ def run_ours(args, workload) -> None:
             "e2e": e2e,
             "gpu_launches": args.steps * launches_per_call,
             "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": roof_unit,
-                         "frac": achieved / peak, "traffic": None,
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(w.name),
                          "peak_source": f"{peak_kind} (burst figure: kernel timed alone)",
                          "kernel_ms": kernel_ms},
             "others": others,
