@@ -313,19 +313,46 @@ def run_ours(args, workload) -> None:
     torch._dynamo.reset()
     compiled = torch.compile(w.fn(), backend=loopfuse_backend, dynamic=True)
 
-    def e2e_step():
-        dev_in = [t.to(dev, non_blocking=True) for t in host_in]
-        out = compiled(*dev_in)
-        host_out.copy_(out.view(host_out.shape), non_blocking=True)
+    # Three streams, two buffer sets: the H2D copy of step i+1 and the D2H copy of step i-1
+    # overlap the kernel of step i (PCIe is full duplex). Every step still copies its own inputs
+    # in and its own result out inside the timed region.
+    cur = torch.cuda.current_stream(dev)
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    dev_in = [[torch.empty_like(t, device=dev) for t in host_in] for _ in range(2)]
+    host_outs = [host_out, torch.empty_like(host_out).pin_memory()]
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_done = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
 
-    for _ in range(3):
-        e2e_step()
+    def e2e_run(n):
+        for i in range(n):
+            k = i % 2
+            with torch.cuda.stream(s_in):
+                if i >= 2:
+                    s_in.wait_event(ev_done[k])      # the kernel of step i-2 has read buffer k
+                for d, h_ in zip(dev_in[k], host_in):
+                    d.copy_(h_, non_blocking=True)
+                ev_in[k].record(s_in)
+            cur.wait_event(ev_in[k])
+            out = compiled(*dev_in[k])
+            ev_done[k].record(cur)
+            out.record_stream(s_out)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_done[k])
+                if i >= 2:
+                    s_out.wait_event(ev_out[k])
+                host_outs[k].copy_(out.view(host_out.shape), non_blocking=True)
+                ev_out[k].record(s_out)
+        cur.wait_stream(s_out)
+        cur.wait_stream(s_in)
+
+    cur.wait_stream(torch.cuda.current_stream(dev))
+    e2e_run(3)
     barrier()
     e2e_steps = max(3, min(args.steps, 10))
     s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s2.record()
-    for _ in range(e2e_steps):
-        e2e_step()
+    e2e_run(e2e_steps)
     e2.record()
     barrier()
     t = torch.tensor([s2.elapsed_time(e2)], device=dev, dtype=torch.float64)

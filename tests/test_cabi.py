@@ -57,6 +57,9 @@ def test_argument_validation_needs_no_gpu(native_lib):
         d.q_stride[i] = d.o_stride[i] = s
         d.k_stride[i] = d.v_stride[i] = s
     assert native_lib.lf_decode_bf16(C.byref(d), None) == -4        # no workspace
+    d.splits = 33
+    assert native_lib.lf_decode_bf16(C.byref(d), None) == -7        # more than 32 splits
+    d.splits = 2
     assert native_lib.lf_decode_paged_bf16(C.byref(d), None) == -1  # no block table
 
 

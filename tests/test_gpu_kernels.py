@@ -81,6 +81,30 @@ def test_decode_config4_full_size_sample():
     assert max_err(out.view_as(want), want) <= TOL
 
 
+def test_combine_entry_point_merges_partials():
+    """lf_combine_f32 on hand-made partials: equals the log-sum-exp merge computed in fp32."""
+    import ctypes as C
+    from loopfuse_b200 import _native
+    B, Hkv, G, D, splits = 2, 3, 4, 128, 5
+    units = B * Hkv * G
+    g = torch.Generator().manual_seed(4)
+    part_o = torch.randn(units, splits, D, generator=g)
+    m = torch.randn(units, splits, generator=g) * 3
+    l = torch.rand(units, splits, generator=g) + 0.5
+    m[0, 2] = float("-inf")          # an empty split contributes nothing
+    l[0, 2] = 0.0
+    part_o[0, 2] = 0.0
+    w = torch.exp2(m - m.max(dim=1, keepdim=True).values)
+    want = (part_o * w[..., None]).sum(1) / (l * w).sum(1, keepdim=True)
+    po, ml = part_o.to(DEV), torch.stack([m, l], dim=-1).contiguous().to(DEV)
+    out = torch.empty(B, Hkv, G, D, dtype=torch.bfloat16, device=DEV)
+    strides = (C.c_int64 * 3)(*out.stride()[:3])
+    rc = _native.load().lf_combine_f32(po.data_ptr(), ml.data_ptr(), out.data_ptr(), B, Hkv, G, D,
+                                       splits, strides, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    assert max_err(out.view(units, D), want) <= TOL
+
+
 # ------------------------------------------------------------------------------------------
 # paged decode
 # ------------------------------------------------------------------------------------------
