@@ -182,8 +182,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Wait limit of a bounded mbarrier wait, in SM clock cycles (about two seconds).
-constexpr long long kWaitLimitCycles = 4000000000ll;
+// Non-blocking probe of a phase.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Wait limit of a bounded mbarrier wait, in SM clock cycles (about 0.2 s; no legitimate wait
+// inside one CTA comes near it).
+constexpr long long kWaitLimitCycles = 400000000ll;
 
 // Bounded wait. Returns false when the limit ran out: the caller records a status code and
 // leaves its role loop, so the kernel still terminates and frees its tensor memory.
@@ -237,12 +253,6 @@ __device__ __forceinline__ void tc_fence_before() {
 }
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void set_max_regs_inc_224() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
-}
-__device__ __forceinline__ void set_max_regs_dec_64() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
 }
 __device__ __forceinline__ void tmem_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");

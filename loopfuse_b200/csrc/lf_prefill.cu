@@ -33,13 +33,16 @@
 #include <math.h>
 
 #include <mutex>
+#include <type_traits>
 
 namespace lf {
 
 constexpr int kTileQ = LF_PREFILL_TILE_Q;
 constexpr int kTileK = LF_PREFILL_TILE_K;
 static_assert(kTileQ == 128 && kTileK == 64, "the kernel is written for 128 x 64 tiles");
-constexpr int kPrefillThreads = 352;
+// Threads per CTA: the softmax warps (8, or 16 in the bounded-score mode), one producer warp and
+// two MMA-issuer warps.
+constexpr int prefill_threads(int mode) { return mode == 3 ? 19 * 32 : 11 * 32; }
 constexpr int kMaxStages = 16;
 constexpr uint32_t kStageBytesTotal = 8 * 2048;
 // K/V ring depth in stages of two 64-key tiles: 4 x 32 KB at D=128, 8 x 16 KB at D=64 (which
@@ -59,6 +62,14 @@ constexpr float kTanhPoly3Limit = 0.4f;
 constexpr int kModeNone = 0;     // logit2 = raw * c2
 constexpr int kModeSoftcap = 1;  // logit2 = tanh(raw * a) * c2
 constexpr int kModeGeneric = 2;  // logit2 = mods(raw * a) * c2
+// Softcap whose output range is small enough (|c2| <= kBoundedMaxC2) that exp2(logit2) can be
+// taken against the fixed reference 0 instead of a running row max: every P lies in
+// [2^-80, 2^80], row sums and O stay far inside the fp32 range, and bf16 keeps the same relative
+// precision at any magnitude. Without a running max the blocks of a row are independent, there
+// is no O rescale, and a row can be split between two threads with no exchange but the final
+// row sum.
+constexpr int kModeBounded = 3;
+constexpr float kBoundedMaxC2 = 80.f;
 
 struct PrefillParams {
   __nv_bfloat16* out;
@@ -68,6 +79,8 @@ struct PrefillParams {
   int32_t n_qtiles;  // ceil(Sq / 128)
   float a;           // multiplies the raw dot product before the score function
   float c2;          // multiplies the score-function output; includes log2(e); > 0
+  float qc[4];       // bounded mode: tanh polynomial in raw^2, scaled to give logit2 / raw
+  float ylim[2];     // bounded mode: validity limits of the two polynomials, on raw^2
   ModChain mods;
   int32_t* status;
   int32_t* dbg_ranges;
@@ -82,6 +95,7 @@ struct __align__(8) PrefillBarriers {
   uint64_t p_full[2][2];   // [tile][buffer]  softmax -> MMA
   uint64_t pv_done[2];     // [tile] one completion per PV
   uint64_t o_final[2];     // [tile] last PV done
+  uint64_t l_ready[2];     // [tile] bounded mode: both halves of every row sum are published
   uint32_t tmem_base;
   uint32_t pad;
 };
@@ -119,7 +133,7 @@ __device__ __forceinline__ void report_timeout(int32_t* status, int where) {
 }
 
 template <int D, int MODE>
-__global__ void __launch_bounds__(kPrefillThreads, 1)
+__global__ void __launch_bounds__(prefill_threads(MODE), 1)
     prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
                    const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
@@ -132,6 +146,10 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
   constexpr uint32_t kIdescQK = make_idesc_bf16(128, kTileK, 0);
   constexpr uint32_t kIdescPV = make_idesc_bf16(128, D, 1);
   constexpr uint32_t kColO = 256;
+  constexpr bool kSplit = MODE == kModeBounded;  // two threads per score row
+  constexpr int kSoftmaxWarps = kSplit ? 16 : 8;
+  constexpr int kProducerWarp = kSoftmaxWarps;
+  constexpr int kMmaWarp0 = kSoftmaxWarps + 1;
 
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -171,7 +189,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
   }
 
   // ---------------- setup ----------------
-  if (warp == 9 && lane == 0) {
+  if (warp == kMmaWarp0 && lane == 0) {
     mbar_init(&bars->q_full[0], 1);
     mbar_init(&bars->q_full[1], 1);
     for (int s = 0; s < kStages; ++s) {
@@ -181,14 +199,15 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     for (int t = 0; t < 2; ++t) {
       for (int bf = 0; bf < 2; ++bf) {
         mbar_init(&bars->s_full[t][bf], 1);
-        mbar_init(&bars->p_full[t][bf], 128);
+        mbar_init(&bars->p_full[t][bf], kSplit ? 256 : 128);
       }
       mbar_init(&bars->pv_done[t], 1);
       mbar_init(&bars->o_final[t], 1);
+      mbar_init(&bars->l_ready[t], 256);
     }
     mbar_fence_init();
   }
-  if (warp == 8 && lane == 0) {
+  if (warp == kProducerWarp && lane == 0) {
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
@@ -202,7 +221,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
 
-  if (warp == 8) {
+  if (warp == kProducerWarp) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       LF_TRACE_DECL(3, true);
@@ -250,13 +269,13 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       }
       LF_TRACE_END();
     }
-  } else if (warp == 9 || warp == 10) {
-    // ---------------- MMA issuers: warp 9 drives query tile 0, warp 10 query tile 1 ----------
+  } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
+    // ---------------- MMA issuers: one warp per query tile ----------
     // Two issuing threads halve the per-instruction issue overhead; the tensor pipe serialises
     // the two independent streams. Both walk the same K/V ring and both release every stage
     // (kv_empty counts two arrivals), whether or not their tile used it.
     if (lane == 0 && hi > lo) {
-      const int t = warp - 9;
+      const int t = warp - kMmaWarp0;
       bool ok = true;
       LF_TRACE_DECL(2, t == 0);
       LF_TRACE_EV(0);
@@ -305,7 +324,10 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         const uint32_t a = s_col + (kt & 1) * 64;
 #pragma unroll
         for (int ks = 0; ks < kTileK / 16; ++ks) {
-          mma_ts(o_col, a + ks * 8, vd + static_cast<uint64_t>(ks * (2048 >> 4)), kIdescPV,
+          // P columns of 16 keys: contiguous, or (bounded mode) 16 columns at the start of each
+          // 32-column half of the S buffer.
+          const uint32_t pa = kSplit ? a + (ks >> 1) * 32 + (ks & 1) * 8 : a + ks * 8;
+          mma_ts(o_col, pa, vd + static_cast<uint64_t>(ks * (2048 >> 4)), kIdescPV,
                  (kt > 0 || ks > 0) ? 1u : 0u);
         }
       };
@@ -348,6 +370,252 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         LF_TRACE_EV(15);
       }
       LF_TRACE_END();
+    }
+  } else if constexpr (kSplit) {
+    // ---------------- softmax warps, bounded-score mode ----------------
+    // Four warpgroups: query tile t = warpgroup / 2; inside a tile, warpgroup `half` takes
+    // columns [32*half, 32*half + 32) of every 64-key block, one thread per (row, half). With
+    // the fixed reference there is no running max, no rescale of O and nothing to exchange
+    // between the two threads of a row until the final row sum.
+    const int wg = warp >> 2;
+    const int t = wg >> 1;
+    const int half = wg & 1;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;  // row inside the tile == tensor-memory lane
+    const int grow = (iq0 + t) * kTileQ + row;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_base = tmem_base + lane_addr + t * 128 + half * 32;
+    const uint32_t o_addr = tmem_base + lane_addr + kColO + t * 128;
+    float* l_slots = reinterpret_cast<float*>(sStage) + t * 256;  // [half][row]
+
+#ifndef LF_TRACE
+    if (p.dbg_ranges && tile_valid[t] && row == 0 && half == 0) {
+      const int64_t idx = ((static_cast<int64_t>(b) * p.Hq + h) * p.n_qtiles + (iq0 + t)) * 2;
+      p.dbg_ranges[idx] = lo_t[t];
+      p.dbg_ranges[idx + 1] = hi_t[t];
+    }
+#endif
+
+    if (has_work[t]) {
+      // Visible column interval of this row: [c_lo, c_hi].
+      int c_hi = p.Skv - 1;
+      int c_lo = 0;
+      if (p.mask_kind != LF_MASK_NONE) c_hi = min(c_hi, grow + p.causal_offset);
+      if (p.mask_kind == LF_MASK_CAUSAL_WINDOW)
+        c_lo = max(0, grow + p.causal_offset - (p.window - 1));
+
+      float l_run = 0.f;
+      bool ok = true;
+      const int nblk = hi_t[t] - lo_t[t];
+      // tanh(x) = x*(1 + y*(-1/3 + y*(2/15 + y*(-17/315)))), y = x^2, x = a*raw. The powers of a
+      // and the output factor c2 are folded into the coefficients p.qc[] on the host, so the
+      // polynomial runs on raw^2 and gives logit2 = raw * q(raw^2) directly; p.ylim[] are the
+      // limits of the two polynomials as bounds on raw^2.
+      const uint64_t q0c = pack2(p.qc[0], p.qc[0]);
+      const uint64_t q1c = pack2(p.qc[1], p.qc[1]);
+      // exp2 on the FMA pipe for one pair in four (see the one-thread-per-row code below).
+      const uint64_t magic2 = pack2(12582912.f, 12582912.f);
+      const uint64_t neg_magic2 = pack2(-12582912.f, -12582912.f);
+      const uint64_t minus_one2 = pack2(-1.f, -1.f);
+      const uint64_t e0 = pack2(0.99992811f, 0.99992811f), e1 = pack2(0.69326099f, 0.69326099f);
+      const uint64_t e2 = pack2(0.24261054f, 0.24261054f), e3 = pack2(0.05517132f, 0.05517132f);
+      // The tanh evaluation (0: degree 3, 1: degree 7, 2: MUFU) is chosen speculatively: a
+      // block starts with what the warp's previous block needed, and is redone on the spot
+      // with a stronger one if its own max |x| (known after the pass) asks for it.
+      int path = 0;
+      LF_TRACE_DECL(t, half == 0 && quarter == 0 && lane == 0);
+      for (int k = 0; k < nblk; ++k) {
+        const int c0 = (lo_t[t] + k) * kTileK + half * 32;  // first key column of this thread
+        const int buf = k & 1;
+        const uint32_t s_addr = s_base + buf * 64;
+        LF_TRACE_EV(20);
+        if (!mbar_wait(&bars->s_full[t][buf], (k >> 1) & 1)) {
+          report_timeout(p.status, 8 + t);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        LF_TRACE_EV(21);
+        const int rel_lo = c_lo - c0;  // visible columns of this thread's 32: [rel_lo, rel_hi]
+        const int rel_hi = c_hi - c0;
+        const bool masked = rel_lo > 0 || rel_hi < 31;
+
+        uint32_t pk[16];
+        float psum = 0.f;
+        for (;;) {
+          // (Read again from tensor memory when a block is redone: P is stored only at the end.)
+          uint32_t sr[32];
+          tmem_ld_32x32b_x32(s_addr, sr);
+          tmem_wait_ld();
+          LF_TRACE_EV(22);
+          uint64_t psum2[2] = {0ull, 0ull};
+          float ymax0 = 0.f, ymax1 = 0.f;
+          auto finish_pair = [&](uint64_t z2, int i, bool apply_mask) {
+            float z0, z1;
+            unpack2(z2, z0, z1);
+            if (apply_mask) {
+              if (i < rel_lo || i > rel_hi) z0 = -INFINITY;
+              if (i + 1 < rel_lo || i + 1 > rel_hi) z1 = -INFINITY;
+            }
+            float p0, p1;
+            if (((i >> 1) & 3) == 3) {
+              const uint64_t zc2 = pack2(fmaxf(z0, -120.f), fmaxf(z1, -120.f));
+              const uint64_t r2 = add2(zc2, magic2);
+              const uint64_t f2 = fma2(add2(r2, neg_magic2), minus_one2, zc2);
+              uint64_t q2 = fma2(f2, e3, e2);
+              q2 = fma2(q2, f2, e1);
+              q2 = fma2(q2, f2, e0);
+              float q0, q1, r0, r1;
+              unpack2(q2, q0, q1);
+              unpack2(r2, r0, r1);
+              p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23));
+              p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
+              if (apply_mask) {  // the clamp above would leave 2^-120 in a masked position
+                if (z0 == -INFINITY) p0 = 0.f;
+                if (z1 == -INFINITY) p1 = 0.f;
+              }
+            } else {
+              p0 = ex2_approx(z0);
+              p1 = ex2_approx(z1);
+            }
+            // The row sum is taken over the bf16-rounded values that the PV product sees, so that
+            // numerator and denominator carry the same rounding (it matters here because the
+            // largest P of a row is not exactly 1 as it is with a running max).
+            const uint32_t pkv = pack_bf16x2(p0, p1);
+            pk[i >> 1] = pkv;
+            psum2[(i >> 1) & 1] =
+                add2(psum2[(i >> 1) & 1], pack2(__uint_as_float(pkv << 16),
+                                                __uint_as_float(pkv & 0xffff0000u)));
+          };
+          auto body = [&](auto path_tag, bool apply_mask) {
+            constexpr int kPath = decltype(path_tag)::value;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const uint64_t r2 = pack2u(sr[i], sr[i + 1]);
+              const uint64_t y2 = mul2(r2, r2);
+              float y0, y1;
+              unpack2(y2, y0, y1);
+              if ((i >> 1) & 1) ymax1 = max3(ymax1, y0, y1); else ymax0 = max3(ymax0, y0, y1);
+              uint64_t z2;
+              if constexpr (kPath == 0) {
+                z2 = mul2(r2, fma2(y2, q1c, q0c));
+              } else if constexpr (kPath == 1) {
+                uint64_t q2 = fma2(y2, pack2(p.qc[3], p.qc[3]), pack2(p.qc[2], p.qc[2]));
+                q2 = fma2(q2, y2, q1c);
+                q2 = fma2(q2, y2, q0c);
+                z2 = mul2(r2, q2);
+              } else {
+                const float t0 = tanh_approx(__uint_as_float(sr[i]) * p.a);
+                const float t1 = tanh_approx(__uint_as_float(sr[i + 1]) * p.a);
+                z2 = mul2(pack2(t0, t1), pack2(p.c2, p.c2));
+              }
+              finish_pair(z2, i, apply_mask);
+            }
+          };
+          if (path == 0) {
+            if (masked) body(std::integral_constant<int, 0>{}, true);
+            else body(std::integral_constant<int, 0>{}, false);
+          } else if (path == 1) {
+            if (masked) body(std::integral_constant<int, 1>{}, true);
+            else body(std::integral_constant<int, 1>{}, false);
+          } else {
+            if (masked) body(std::integral_constant<int, 2>{}, true);
+            else body(std::integral_constant<int, 2>{}, false);
+          }
+          float ps[4];
+          unpack2(psum2[0], ps[0], ps[1]);
+          unpack2(psum2[1], ps[2], ps[3]);
+          psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
+          // What this block needed, over the whole warp (masked columns included: their raw
+          // scores are ordinary finite numbers).
+          const float ymax = fmaxf(ymax0, ymax1);
+          const unsigned mine = ymax > p.ylim[1] ? 2u : (ymax > p.ylim[0] ? 1u : 0u);
+          const int needed = static_cast<int>(__reduce_max_sync(0xffffffffu, mine));
+          const bool redo = needed > path;
+          path = needed;
+          if (!redo) break;
+        }
+        l_run += psum;
+        LF_TRACE_EV(24);
+        // P (bf16, two per column) goes on top of the first 16 of this thread's S columns.
+        tmem_st_32x32b_x16(s_addr, pk);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&bars->p_full[t][buf]);
+        LF_TRACE_EV(25);
+      }
+      LF_TRACE_EV(26);
+
+      // Row sum: the two halves meet in shared memory.
+      if (ok) {
+        l_slots[half * 128 + row] = l_run;
+        mbar_arrive(&bars->l_ready[t]);
+        if (!mbar_wait(&bars->l_ready[t], 0)) {
+          report_timeout(p.status, 18 + t);
+          ok = false;
+        }
+        l_run = l_slots[row] + l_slots[128 + row];
+      }
+      // Epilogue: O_t / l -> bf16 -> global; each half writes D/2 of the row's columns.
+      if (ok) {
+        if (!mbar_wait(&bars->o_final[t], 0)) {
+          report_timeout(p.status, 10 + t);
+          ok = false;
+        }
+      }
+      if (ok) {
+        tc_fence_after();
+        const float inv = 1.f / l_run;
+        // Each warp owns 32 rows. A 32-column chunk (64 bytes per row) goes through a swizzled
+        // 2 KB buffer of the warp so that one store instruction writes eight 64-byte row
+        // segments instead of thirty-two 16-byte pieces. The buffers sit in the tile's own Q
+        // area, which nothing reads once the last MMA of the tile has completed.
+        unsigned char* stage = sQ + t * kQTileBytes + (warp & 7) * 2048;
+        __nv_bfloat16* obase = p.out + b * p.o_stride[0] + h * p.o_stride[1];
+        const int row0 = (iq0 + t) * kTileQ + quarter * 32;  // first global row of the warp
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          const int col = half * (D / 2) + c * 32;
+          uint32_t orr[32];
+          tmem_ld_32x32b_x32(o_addr + col, orr);
+          tmem_wait_ld();
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {  // piece q of row r sits at position q ^ ((r >> 1) & 3)
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(orr[8 * q]) * inv,
+                              __uint_as_float(orr[8 * q + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(orr[8 * q + 2]) * inv,
+                              __uint_as_float(orr[8 * q + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(orr[8 * q + 4]) * inv,
+                              __uint_as_float(orr[8 * q + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(orr[8 * q + 6]) * inv,
+                              __uint_as_float(orr[8 * q + 7]) * inv);
+            *reinterpret_cast<uint4*>(stage + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) = w;
+          }
+          __syncwarp();
+#pragma unroll
+          for (int rr = 0; rr < 4; ++rr) {
+            const int r = rr * 8 + (lane >> 2);
+            const int q = lane & 3;
+            const uint4 w =
+                *reinterpret_cast<const uint4*>(stage + r * 64 + ((q ^ ((r >> 1) & 3)) << 4));
+            if (row0 + r < p.Sq)
+              *reinterpret_cast<uint4*>(obase + static_cast<int64_t>(row0 + r) * p.o_stride[2] +
+                                        col + q * 8) = w;
+          }
+          __syncwarp();
+        }
+      }
+      LF_TRACE_EV(27);
+      LF_TRACE_END();
+    } else if (tile_valid[t] && grow < p.Sq && half == 0) {
+      // No visible key at all for this tile: softmax of an all -inf row is NaN in the
+      // eager computation, so the rows are written as NaN.
+      __nv_bfloat16* orow = p.out + b * p.o_stride[0] + h * p.o_stride[1] +
+                            static_cast<int64_t>(grow) * p.o_stride[2];
+      const uint4 nan4 = {0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u};
+#pragma unroll
+      for (int c = 0; c < D; c += 8) *reinterpret_cast<uint4*>(orow + c) = nan4;
     }
   } else {
     // ---------------- softmax warps ----------------
@@ -754,7 +1022,7 @@ static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CU
   }
   const int pairs = (p.n_qtiles + 1) / 2;
   dim3 grid(pairs, p.Hq, B);
-  prefill_kernel<D, MODE><<<grid, kPrefillThreads, smem, st>>>(mq, mk, mv, p);
+  prefill_kernel<D, MODE><<<grid, prefill_threads(MODE), smem, st>>>(mq, mk, mv, p);
   return check_launch("prefill_kernel");
 }
 
@@ -788,6 +1056,8 @@ static int prefill_impl(const LfPrefillArgs* a, void* stream) {
   p.n_qtiles = (a->Sq + kTileQ - 1) / kTileQ;
   p.status = a->status;
   p.dbg_ranges = a->dbg_ranges;
+  for (int i = 0; i < 4; ++i) p.qc[i] = 0.f;
+  p.ylim[0] = p.ylim[1] = 0.f;
   p.mods.n = 0;
   for (int i = 0; i < LF_MAX_MODS; ++i) {
     p.mods.op[i] = 0;
@@ -818,9 +1088,18 @@ static int prefill_impl(const LfPrefillArgs* a, void* stream) {
         ++j;
       }
       if (j == a->n_mod && post > 0.f) {
-        mode = kModeSoftcap;
         p.a = pre;
         p.c2 = post * kLog2eF;
+        // |logit2| <= c2: small enough for the fixed softmax reference (the row sum of up to
+        // 2^22 terms of at most 2^80 stays far below the fp32 limit).
+        mode = (p.c2 <= kBoundedMaxC2 && a->Skv <= (1 << 22)) ? kModeBounded : kModeSoftcap;
+        const float a2 = p.a * p.a, k0 = p.a * p.c2;
+        p.qc[0] = k0;
+        p.qc[1] = k0 * a2 * (-1.f / 3.f);
+        p.qc[2] = k0 * a2 * a2 * (2.f / 15.f);
+        p.qc[3] = k0 * a2 * a2 * a2 * (-17.f / 315.f);
+        p.ylim[0] = kTanhPoly1Limit * kTanhPoly1Limit / a2;
+        p.ylim[1] = kTanhPoly3Limit * kTanhPoly3Limit / a2;
       }
     }
     if (mode == kModeGeneric) {
@@ -846,10 +1125,12 @@ static int prefill_impl(const LfPrefillArgs* a, void* stream) {
   if (a->D == 128) {
     if (mode == kModeNone) return launch_prefill<128, kModeNone>(mq, mk, mv, p, a->B, st);
     if (mode == kModeSoftcap) return launch_prefill<128, kModeSoftcap>(mq, mk, mv, p, a->B, st);
+    if (mode == kModeBounded) return launch_prefill<128, kModeBounded>(mq, mk, mv, p, a->B, st);
     return launch_prefill<128, kModeGeneric>(mq, mk, mv, p, a->B, st);
   }
   if (mode == kModeNone) return launch_prefill<64, kModeNone>(mq, mk, mv, p, a->B, st);
   if (mode == kModeSoftcap) return launch_prefill<64, kModeSoftcap>(mq, mk, mv, p, a->B, st);
+  if (mode == kModeBounded) return launch_prefill<64, kModeBounded>(mq, mk, mv, p, a->B, st);
   return launch_prefill<64, kModeGeneric>(mq, mk, mv, p, a->B, st);
 }
 
