@@ -4,22 +4,29 @@
 // One CTA owns two consecutive 128-row query tiles of one (batch, q head) and walks the 64-key
 // KV tiles that the skip range leaves (fully masked tiles are never loaded or multiplied).
 //
+// Running-max modes (plain scores, generic score mods, softcap with a large cap), 352 threads:
 //   warps 0-3   softmax for query tile 0 (one thread per score row)
 //   warps 4-7   softmax for query tile 1
 //   warp  8     TMA producer: Q tiles once, then pairs of K/V tiles into a ring, in the order
 //               the MMA warps consume them: {K(lo), K(lo+1)}, {V(lo), K(lo+2)}, {V(lo+1), ...
 //   warp  9/10  MMA issuers (one thread each, one per query tile): S_t[buf] = Q_t K^T,
 //               O_t += P_t V
+// Bounded-score mode (softcap whose output range needs no running max), 672 threads:
+//   warps 0-7   softmax for query tile 0: two threads per score row, 32 columns of a block each
+//   warps 8-15  softmax for query tile 1
+//   warp  16    TMA producer (same ring)
+//   warps 17/18 PV issuers of tile 0 / 1, warps 19/20 QK^T issuers of tile 0 / 1
 //
 // Tensor memory (512 columns x 128 lanes of 32 bit):
 //   tile t, buffer b: S at column t*128 + b*64 (64 fp32 columns); P (bf16, two per column)
-//   overwrites the first 32 columns of its S buffer.   O_t at column 256 + t*128 (D columns).
+//   overwrites the first 32 columns of its S buffer (bounded mode: the first 16 columns of each
+//   32-column half).   O_t at column 256 + t*128 (D columns).
 //
 // S is double-buffered per query tile: QK^T of KV tile j+2 is issued right after PV of tile j,
 // so the tensor pipe computes the next scores while the softmax warps work on the current
-// ones; the only dependency left between the two sides is "PV(j) needs P(j)". The softmax warps
-// rescale O_t in place when the running max moves by more than 2^8 (rare); "S(k+1) is ready"
-// tells them that PV(k-1) is complete.
+// ones; the only dependency left between the two sides is "PV(j) needs P(j)". In the
+// running-max modes the softmax warps rescale O_t in place when the max moves by more than 2^8
+// (rare); "S(k+1) is ready" tells them that PV(k-1) is complete.
 //
 // Shared-memory tiles use the 128-byte swizzle that TMA writes and the MMA descriptors read:
 // a [rows][D] bf16 tile is stored as D/64 blocks of [rows][64] (128-byte rows).
@@ -40,9 +47,9 @@ namespace lf {
 constexpr int kTileQ = LF_PREFILL_TILE_Q;
 constexpr int kTileK = LF_PREFILL_TILE_K;
 static_assert(kTileQ == 128 && kTileK == 64, "the kernel is written for 128 x 64 tiles");
-// Threads per CTA: the softmax warps (8, or 16 in the bounded-score mode), one producer warp and
-// two MMA-issuer warps.
-constexpr int prefill_threads(int mode) { return mode == 3 ? 19 * 32 : 11 * 32; }
+// Threads per CTA: the softmax warps, one producer warp and the MMA-issuer warps (8 + 1 + 2, or
+// 16 + 1 + 4 in the bounded-score mode).
+constexpr int prefill_threads(int mode) { return mode == 3 ? 21 * 32 : 11 * 32; }
 constexpr int kMaxStages = 16;
 constexpr uint32_t kStageBytesTotal = 8 * 2048;
 // K/V ring depth in stages of two 64-key tiles: 4 x 32 KB at D=128, 8 x 16 KB at D=64 (which
@@ -93,7 +100,8 @@ struct __align__(8) PrefillBarriers {
   uint64_t kv_empty[kMaxStages];
   uint64_t s_full[2][2];   // [tile][buffer]  MMA -> softmax
   uint64_t p_full[2][2];   // [tile][buffer]  softmax -> MMA
-  uint64_t pv_done[2];     // [tile] one completion per PV
+  uint64_t pv_done[2];     // [tile] second-to-last PV done (running-max modes)
+  uint64_t pv_each[2][2];  // [tile][buffer] bounded mode: PV of the block in that buffer done
   uint64_t o_final[2];     // [tile] last PV done
   uint64_t l_ready[2];     // [tile] bounded mode: both halves of every row sum are published
   uint32_t tmem_base;
@@ -199,9 +207,11 @@ __global__ void __launch_bounds__(prefill_threads(MODE), 1)
     for (int t = 0; t < 2; ++t) {
       for (int bf = 0; bf < 2; ++bf) {
         mbar_init(&bars->s_full[t][bf], 1);
-        mbar_init(&bars->p_full[t][bf], kSplit ? 256 : 128);
+        mbar_init(&bars->p_full[t][bf], kSplit ? 8 : 128);  // split: one arrival per warp
       }
       mbar_init(&bars->pv_done[t], 1);
+      mbar_init(&bars->pv_each[t][0], 1);
+      mbar_init(&bars->pv_each[t][1], 1);
       mbar_init(&bars->o_final[t], 1);
       mbar_init(&bars->l_ready[t], 256);
     }
@@ -269,7 +279,121 @@ __global__ void __launch_bounds__(prefill_threads(MODE), 1)
       }
       LF_TRACE_END();
     }
-  } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
+  } else if (kSplit && warp >= kMmaWarp0 && warp < kMmaWarp0 + 4) {
+    // ---------------- MMA issuers, bounded mode: two warps per query tile ----------
+    // In this mode the softmax is fast enough that instruction issue of the MMA side limits the
+    // loop (a thread sustains roughly one tcgen05.mma per 100 cycles next to the softmax warps),
+    // so each tile has one thread for O_t += P V (4 instructions per block) and one for
+    // S_t = Q_t K^T (8 per block). The scores of block j+2 overwrite the buffer that held
+    // P(j), so the QK thread waits for the completion of PV(j) (`pv_each`). A ring stage
+    // {V(j), K(j+2)} is released by the QK thread when it multiplies K(j+2) (PV(j) is complete
+    // by then), otherwise by the PV thread.
+    if (lane == 0 && hi > lo) {
+      const int t = (warp - kMmaWarp0) & 1;
+      const bool is_qk = warp - kMmaWarp0 >= 2;
+      bool ok = true;
+      LF_TRACE_DECL(2, t == 0 && is_qk);
+      LF_TRACE_EV(0);
+      constexpr uint32_t kStageUnits = (2 * kKVTileBytes) >> 4;  // a stage is a pair of tiles
+      constexpr uint32_t kHalfUnits = kKVTileBytes >> 4;
+      const uint32_t s_col = tmem_base + t * 128;
+      const uint32_t o_col = tmem_base + kColO + t * 128;
+      auto active = [&](int j) { return has_work[t] && j >= lo_t[t] && j < hi_t[t]; };
+      int n = 0;  // ring position, walks the same sequence as the producer
+      auto wait_stage = [&](int where) -> int {  // next ring stage, waited full; -1 on time-out
+        const int stage = n % kStages;
+        const uint32_t parity = (n / kStages) & 1;
+        ++n;
+        if (!mbar_wait(&bars->kv_full[stage], parity)) {
+          report_timeout(p.status, where);
+          ok = false;
+          return -1;
+        }
+        return stage;
+      };
+      if (is_qk) {
+        if (has_work[t] && !mbar_wait(&bars->q_full[t], 0)) {
+          report_timeout(p.status, 2);
+          ok = false;
+        }
+        const uint64_t qdesc = make_smem_desc_sw128(smem_u32(sQ) + t * kQTileBytes, 16, 1024);
+        const uint64_t kdesc0 = make_smem_desc_sw128(smem_u32(sKV), 16, 1024);
+        auto issue_qk = [&](int stage, int hf, int j) {
+          const int buf = (j - lo_t[t]) & 1;
+          const uint64_t kd =
+              kdesc0 + static_cast<uint64_t>(stage * kStageUnits + hf * kHalfUnits);
+          const uint32_t d = s_col + buf * 64;
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks) {
+            mma_ss(d, qdesc + static_cast<uint64_t>((ks / 4) * (kQBlockBytes >> 4) + (ks % 4) * 2),
+                   kd + static_cast<uint64_t>((ks / 4) * (kKVBlockBytes >> 4) + (ks % 4) * 2),
+                   kIdescQK, ks > 0 ? 1u : 0u);
+          }
+          tc_commit(&bars->s_full[t][buf]);
+        };
+        // Prologue: scores of the first two KV tiles (one stage).
+        if (ok) {
+          const int stage = wait_stage(3);
+          if (stage >= 0) {
+            tc_fence_after();
+            if (active(lo)) issue_qk(stage, 0, lo);
+            if (lo + 1 < hi && active(lo + 1)) issue_qk(stage, 1, lo + 1);
+            tc_commit(&bars->kv_empty[stage]);
+          }
+        }
+        for (int j = lo; j < hi && ok; ++j) {
+          LF_TRACE_EV(10);
+          const int st = wait_stage(4);  // {V(j), K(j+2)}
+          if (st < 0) break;
+          LF_TRACE_EV(11);
+          if (j + 2 < hi && active(j + 2)) {
+            if (active(j)) {
+              const int kt = j - lo_t[t];
+              if (!mbar_wait(&bars->pv_each[t][kt & 1], (kt >> 1) & 1)) {
+                report_timeout(p.status, 12 + t);
+                ok = false;
+                break;
+              }
+            }
+            tc_fence_after();
+            LF_TRACE_EV(13);
+            issue_qk(st, 1, j + 2);
+            tc_commit(&bars->kv_empty[st]);
+          }
+          LF_TRACE_EV(15);
+        }
+      } else {
+        const uint64_t vdesc0 = make_smem_desc_sw128(smem_u32(sKV), kKVBlockBytes, 1024);
+        n = 1;  // the first stage holds K tiles only
+        for (int j = lo; j < hi && ok; ++j) {
+          const int st = wait_stage(5);  // {V(j), K(j+2)}
+          if (st < 0) break;
+          if (active(j)) {
+            const int kt = j - lo_t[t];
+            if (!mbar_wait(&bars->p_full[t][kt & 1], (kt >> 1) & 1)) {
+              report_timeout(p.status, 6 + t);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint64_t vd = vdesc0 + static_cast<uint64_t>(st * kStageUnits);
+            const uint32_t a = s_col + (kt & 1) * 64;
+#pragma unroll
+            for (int ks = 0; ks < kTileK / 16; ++ks) {
+              // P columns of 16 keys: 16 columns at the start of each 32-column half of S.
+              mma_ts(o_col, a + (ks >> 1) * 32 + (ks & 1) * 8,
+                     vd + static_cast<uint64_t>(ks * (2048 >> 4)), kIdescPV,
+                     (kt > 0 || ks > 0) ? 1u : 0u);
+            }
+            tc_commit(&bars->pv_each[t][kt & 1]);
+            if (j == hi_t[t] - 1) tc_commit(&bars->o_final[t]);
+          }
+          if (!(j + 2 < hi && active(j + 2))) tc_commit(&bars->kv_empty[st]);
+        }
+      }
+      LF_TRACE_END();
+    }
+  } else if (!kSplit && (warp == kMmaWarp0 || warp == kMmaWarp0 + 1)) {
     // ---------------- MMA issuers: one warp per query tile ----------
     // Two issuing threads halve the per-instruction issue overhead; the tensor pipe serialises
     // the two independent streams. Both walk the same K/V ring and both release every stage
@@ -324,10 +448,7 @@ __global__ void __launch_bounds__(prefill_threads(MODE), 1)
         const uint32_t a = s_col + (kt & 1) * 64;
 #pragma unroll
         for (int ks = 0; ks < kTileK / 16; ++ks) {
-          // P columns of 16 keys: contiguous, or (bounded mode) 16 columns at the start of each
-          // 32-column half of the S buffer.
-          const uint32_t pa = kSplit ? a + (ks >> 1) * 32 + (ks & 1) * 8 : a + ks * 8;
-          mma_ts(o_col, pa, vd + static_cast<uint64_t>(ks * (2048 >> 4)), kIdescPV,
+          mma_ts(o_col, a + ks * 8, vd + static_cast<uint64_t>(ks * (2048 >> 4)), kIdescPV,
                  (kt > 0 || ks > 0) ? 1u : 0u);
         }
       };
@@ -541,7 +662,9 @@ __global__ void __launch_bounds__(prefill_threads(MODE), 1)
         tmem_st_32x32b_x16(s_addr, pk);
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(&bars->p_full[t][buf]);
+        // One arrival per warp (256 arrivals on one barrier word would serialise).
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->p_full[t][buf]);
         LF_TRACE_EV(25);
       }
       LF_TRACE_EV(26);
