@@ -93,6 +93,13 @@ __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
   return r;
 }
+// acc_lo += low bf16 half of v, acc_hi += high half (mixed-precision add, exact conversion).
+__device__ __forceinline__ void add_bf16x2_to_f32(float& acc_lo, float& acc_hi, uint32_t v) {
+  const unsigned short h0 = static_cast<unsigned short>(v & 0xffffu);
+  const unsigned short h1 = static_cast<unsigned short>(v >> 16);
+  asm("add.rn.f32.bf16 %0, %1, %0;" : "+f"(acc_lo) : "h"(h0));
+  asm("add.rn.f32.bf16 %0, %1, %0;" : "+f"(acc_hi) : "h"(h1));
+}
 __device__ __forceinline__ uint64_t pack2u(uint32_t lo, uint32_t hi) {
   uint64_t r;
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));

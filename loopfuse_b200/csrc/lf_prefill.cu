@@ -534,12 +534,6 @@ __global__ void __launch_bounds__(prefill_threads(MODE), 1)
       // limits of the two polynomials as bounds on raw^2.
       const uint64_t q0c = pack2(p.qc[0], p.qc[0]);
       const uint64_t q1c = pack2(p.qc[1], p.qc[1]);
-      // exp2 on the FMA pipe for one pair in four (see the one-thread-per-row code below).
-      const uint64_t magic2 = pack2(12582912.f, 12582912.f);
-      const uint64_t neg_magic2 = pack2(-12582912.f, -12582912.f);
-      const uint64_t minus_one2 = pack2(-1.f, -1.f);
-      const uint64_t e0 = pack2(0.99992811f, 0.99992811f), e1 = pack2(0.69326099f, 0.69326099f);
-      const uint64_t e2 = pack2(0.24261054f, 0.24261054f), e3 = pack2(0.05517132f, 0.05517132f);
       // The tanh evaluation (0: degree 3, 1: degree 7, 2: MUFU) is chosen speculatively: a
       // block starts with what the warp's previous block needed, and is redone on the spot
       // with a stronger one if its own max |x| (known after the pass) asks for it.
@@ -562,14 +556,14 @@ __global__ void __launch_bounds__(prefill_threads(MODE), 1)
         const bool masked = rel_lo > 0 || rel_hi < 31;
 
         uint32_t pk[16];
-        float psum = 0.f;
+        float block_sum = 0.f;
         for (;;) {
           // (Read again from tensor memory when a block is redone: P is stored only at the end.)
           uint32_t sr[32];
           tmem_ld_32x32b_x32(s_addr, sr);
           tmem_wait_ld();
           LF_TRACE_EV(22);
-          uint64_t psum2[2] = {0ull, 0ull};
+          float psum[4] = {0.f, 0.f, 0.f, 0.f};
           float ymax0 = 0.f, ymax1 = 0.f;
           auto finish_pair = [&](uint64_t z2, int i, bool apply_mask) {
             float z0, z1;
@@ -578,35 +572,16 @@ __global__ void __launch_bounds__(prefill_threads(MODE), 1)
               if (i < rel_lo || i > rel_hi) z0 = -INFINITY;
               if (i + 1 < rel_lo || i + 1 > rel_hi) z1 = -INFINITY;
             }
-            float p0, p1;
-            if (((i >> 1) & 3) == 3) {
-              const uint64_t zc2 = pack2(fmaxf(z0, -120.f), fmaxf(z1, -120.f));
-              const uint64_t r2 = add2(zc2, magic2);
-              const uint64_t f2 = fma2(add2(r2, neg_magic2), minus_one2, zc2);
-              uint64_t q2 = fma2(f2, e3, e2);
-              q2 = fma2(q2, f2, e1);
-              q2 = fma2(q2, f2, e0);
-              float q0, q1, r0, r1;
-              unpack2(q2, q0, q1);
-              unpack2(r2, r0, r1);
-              p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23));
-              p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
-              if (apply_mask) {  // the clamp above would leave 2^-120 in a masked position
-                if (z0 == -INFINITY) p0 = 0.f;
-                if (z1 == -INFINITY) p1 = 0.f;
-              }
-            } else {
-              p0 = ex2_approx(z0);
-              p1 = ex2_approx(z1);
-            }
+            // Every exponential goes to MUFU here: this loop is bound by instruction dispatch,
+            // and two ex2 cost less of it than their FMA-pipe emulation.
+            const uint32_t pkv = pack_bf16x2(ex2_approx(z0), ex2_approx(z1));
+            pk[i >> 1] = pkv;
             // The row sum is taken over the bf16-rounded values that the PV product sees, so that
             // numerator and denominator carry the same rounding (it matters here because the
-            // largest P of a row is not exactly 1 as it is with a running max).
-            const uint32_t pkv = pack_bf16x2(p0, p1);
-            pk[i >> 1] = pkv;
-            psum2[(i >> 1) & 1] =
-                add2(psum2[(i >> 1) & 1], pack2(__uint_as_float(pkv << 16),
-                                                __uint_as_float(pkv & 0xffff0000u)));
+            // largest P of a row is not exactly 1 as it is with a running max). The mixed
+            // precision add reads the bf16 halves directly.
+            if ((i >> 1) & 1) add_bf16x2_to_f32(psum[2], psum[3], pkv);
+            else add_bf16x2_to_f32(psum[0], psum[1], pkv);
           };
           auto body = [&](auto path_tag, bool apply_mask) {
             constexpr int kPath = decltype(path_tag)::value;
@@ -643,10 +618,7 @@ __global__ void __launch_bounds__(prefill_threads(MODE), 1)
             if (masked) body(std::integral_constant<int, 2>{}, true);
             else body(std::integral_constant<int, 2>{}, false);
           }
-          float ps[4];
-          unpack2(psum2[0], ps[0], ps[1]);
-          unpack2(psum2[1], ps[2], ps[3]);
-          psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
+          block_sum = (psum[0] + psum[1]) + (psum[2] + psum[3]);
           // What this block needed, over the whole warp (masked columns included: their raw
           // scores are ordinary finite numbers).
           const float ymax = fmaxf(ymax0, ymax1);
@@ -656,7 +628,7 @@ __global__ void __launch_bounds__(prefill_threads(MODE), 1)
           path = needed;
           if (!redo) break;
         }
-        l_run += psum;
+        l_run += block_sum;
         LF_TRACE_EV(24);
         // P (bf16, two per column) goes on top of the first 16 of this thread's S columns.
         tmem_st_32x32b_x16(s_addr, pk);
