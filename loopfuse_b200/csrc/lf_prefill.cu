@@ -39,6 +39,7 @@
 #include <cudaTypedefs.h>
 #include <math.h>
 
+#include <atomic>
 #include <mutex>
 #include <type_traits>
 
@@ -91,6 +92,10 @@ struct PrefillParams {
   ModChain mods;
   int32_t* status;
   int32_t* dbg_ranges;
+  // Persistent (bounded-mode) kernel only: the work queue.
+  int32_t n_pairs;       // query-tile pairs per head
+  int32_t n_items;       // n_pairs * Hq * B
+  unsigned int* ticket;  // device counter, zero at launch
 };
 
 // Barrier block at the start of shared memory.
@@ -138,6 +143,9 @@ struct Tracer {
 
 __device__ __forceinline__ void report_timeout(int32_t* status, int where) {
   if (status) atomicCAS(status, LF_DEV_OK, LF_DEV_TIMEOUT | (where << 8));
+#ifdef LF_DIAG_SITES
+  if (status) atomicOr(status + 1, 1 << where);
+#endif
 }
 
 template <int D, int MODE>
@@ -202,7 +210,7 @@ __global__ void __launch_bounds__(prefill_threads(MODE), 1)
     mbar_init(&bars->q_full[1], 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&bars->kv_full[s], 1);
-      mbar_init(&bars->kv_empty[s], 2);
+      mbar_init(&bars->kv_empty[s], kSplit ? 4 : 2);  // one arrival per MMA thread
     }
     for (int t = 0; t < 2; ++t) {
       for (int bf = 0; bf < 2; ++bf) {
@@ -285,9 +293,9 @@ __global__ void __launch_bounds__(prefill_threads(MODE), 1)
     // loop (a thread sustains roughly one tcgen05.mma per 100 cycles next to the softmax warps),
     // so each tile has one thread for O_t += P V (4 instructions per block) and one for
     // S_t = Q_t K^T (8 per block). The scores of block j+2 overwrite the buffer that held
-    // P(j), so the QK thread waits for the completion of PV(j) (`pv_each`). A ring stage
-    // {V(j), K(j+2)} is released by the QK thread when it multiplies K(j+2) (PV(j) is complete
-    // by then), otherwise by the PV thread.
+    // P(j), so the QK thread waits for the completion of PV(j) (`pv_each`). All four threads
+    // walk every ring stage and each releases it (kv_empty counts four arrivals) once the MMAs
+    // it issued from the stage, if any, are complete.
     if (lane == 0 && hi > lo) {
       const int t = (warp - kMmaWarp0) & 1;
       const bool is_qk = warp - kMmaWarp0 >= 2;
@@ -358,13 +366,16 @@ __global__ void __launch_bounds__(prefill_threads(MODE), 1)
             tc_fence_after();
             LF_TRACE_EV(13);
             issue_qk(st, 1, j + 2);
-            tc_commit(&bars->kv_empty[st]);
           }
+          tc_commit(&bars->kv_empty[st]);
           LF_TRACE_EV(15);
         }
       } else {
         const uint64_t vdesc0 = make_smem_desc_sw128(smem_u32(sKV), kKVBlockBytes, 1024);
-        n = 1;  // the first stage holds K tiles only
+        {  // the first stage holds K tiles only
+          const int st = wait_stage(5);
+          if (st >= 0) tc_commit(&bars->kv_empty[st]);
+        }
         for (int j = lo; j < hi && ok; ++j) {
           const int st = wait_stage(5);  // {V(j), K(j+2)}
           if (st < 0) break;
@@ -388,7 +399,7 @@ __global__ void __launch_bounds__(prefill_threads(MODE), 1)
             tc_commit(&bars->pv_each[t][kt & 1]);
             if (j == hi_t[t] - 1) tc_commit(&bars->o_final[t]);
           }
-          if (!(j + 2 < hi && active(j + 2))) tc_commit(&bars->kv_empty[st]);
+          tc_commit(&bars->kv_empty[st]);
         }
       }
       LF_TRACE_END();
@@ -1044,6 +1055,12 @@ __global__ void __launch_bounds__(prefill_threads(MODE), 1)
   }
 }
 
+}  // namespace lf
+
+#include "lf_prefill_bounded.cuh"
+
+namespace lf {
+
 // ---------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------
@@ -1121,6 +1138,53 @@ static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CU
   return check_launch("prefill_kernel");
 }
 
+// Ticket counters of the persistent kernel: a small ring in the library image, so that launching
+// allocates nothing. A launch takes the next slot and zeroes it in stream order; launches that
+// overlap on the GPU use different slots unless more than kTicketSlots are in flight.
+constexpr int kTicketSlots = 256;
+static __device__ unsigned int g_prefill_tickets[kTicketSlots];
+
+template <int D>
+static int launch_prefill_bounded(const CUtensorMap& mq, const CUtensorMap& mk,
+                                  const CUtensorMap& mv, PrefillParams p, int B, cudaStream_t st) {
+  constexpr size_t kQTileBytes = static_cast<size_t>(kTileQ) * D * 2;
+  constexpr size_t kKVTileBytes = static_cast<size_t>(kTileK) * D * 2;
+  constexpr size_t smem = 1024 /*align slack*/ + 1024 /*barriers*/ + kBoundedStageBytes +
+                          2 * kQTileBytes + StagesFor<D>::value * 2 * kKVTileBytes;
+  static thread_local int configured_dev = -1;
+  static thread_local unsigned int* tickets = nullptr;
+  static thread_local int sm_count = 0;
+  static std::atomic<unsigned int> next_slot{0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_dev != dev) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_bounded_kernel<D>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e == cudaSuccess)
+      e = cudaGetSymbolAddress(reinterpret_cast<void**>(&tickets), g_prefill_tickets);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) {
+      set_cuda_error(e, "prefill_bounded_kernel setup");
+      return LF_ERR_CUDA;
+    }
+    configured_dev = dev;
+  }
+  p.n_pairs = (p.n_qtiles + 1) / 2;
+  const int64_t n_items = static_cast<int64_t>(p.n_pairs) * p.Hq * B;
+  if (n_items > 0x7fffffff - 4096) return LF_ERR_TOO_LARGE;
+  p.n_items = static_cast<int32_t>(n_items);
+  p.ticket = tickets + next_slot.fetch_add(1) % kTicketSlots;
+  cudaError_t e = cudaMemsetAsync(p.ticket, 0, sizeof(unsigned int), st);
+  if (e != cudaSuccess) {
+    set_cuda_error(e, "cudaMemsetAsync(ticket)");
+    return LF_ERR_CUDA;
+  }
+  const int grid = static_cast<int>(n_items < sm_count ? n_items : sm_count);
+  prefill_bounded_kernel<D><<<grid, kBoundedThreads, smem, st>>>(mq, mk, mv, p);
+  return check_launch("prefill_bounded_kernel");
+}
+
 static int prefill_impl(const LfPrefillArgs* a, void* stream) {
   if (!a || !a->q || !a->k || !a->v || !a->out) return LF_ERR_INVALID_ARG;
   if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Sq <= 0 || a->Skv <= 0)
@@ -1153,6 +1217,9 @@ static int prefill_impl(const LfPrefillArgs* a, void* stream) {
   p.dbg_ranges = a->dbg_ranges;
   for (int i = 0; i < 4; ++i) p.qc[i] = 0.f;
   p.ylim[0] = p.ylim[1] = 0.f;
+  p.n_pairs = 0;
+  p.n_items = 0;
+  p.ticket = nullptr;
   p.mods.n = 0;
   for (int i = 0; i < LF_MAX_MODS; ++i) {
     p.mods.op[i] = 0;
@@ -1220,11 +1287,17 @@ static int prefill_impl(const LfPrefillArgs* a, void* stream) {
   if (a->D == 128) {
     if (mode == kModeNone) return launch_prefill<128, kModeNone>(mq, mk, mv, p, a->B, st);
     if (mode == kModeSoftcap) return launch_prefill<128, kModeSoftcap>(mq, mk, mv, p, a->B, st);
+#ifndef LF_NO_PERSISTENT
+    if (mode == kModeBounded) return launch_prefill_bounded<128>(mq, mk, mv, p, a->B, st);
+#endif
     if (mode == kModeBounded) return launch_prefill<128, kModeBounded>(mq, mk, mv, p, a->B, st);
     return launch_prefill<128, kModeGeneric>(mq, mk, mv, p, a->B, st);
   }
   if (mode == kModeNone) return launch_prefill<64, kModeNone>(mq, mk, mv, p, a->B, st);
   if (mode == kModeSoftcap) return launch_prefill<64, kModeSoftcap>(mq, mk, mv, p, a->B, st);
+#ifndef LF_NO_PERSISTENT
+  if (mode == kModeBounded) return launch_prefill_bounded<64>(mq, mk, mv, p, a->B, st);
+#endif
   if (mode == kModeBounded) return launch_prefill<64, kModeBounded>(mq, mk, mv, p, a->B, st);
   return launch_prefill<64, kModeGeneric>(mq, mk, mv, p, a->B, st);
 }

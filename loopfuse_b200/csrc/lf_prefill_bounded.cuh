@@ -1,0 +1,655 @@
+// Persistent form of the bounded-score prefill kernel (included by lf_prefill.cu).
+//
+// Same tiles, roles and tensor-memory layout as prefill_kernel<D, kModeBounded>, but one CTA per
+// SM walks a queue of work items (one item = two consecutive query tiles of one (batch, head)),
+// taken from a ticket counter in the launch order of the non-persistent grid (the query-tile pairs
+// of one head next to each other, heaviest first, so that they run at the same time on different
+// SMs and share K/V through L2). Nothing drains between items:
+//   - the K/V ring just continues with the next item's tiles;
+//   - the S buffers of a tile keep alternating (buffer = running block count of the tile & 1), so
+//     the first scores of the next item are computed while the last blocks of this one are still
+//     in their softmax;
+//   - Q_t of the next item is fetched as soon as the last QK^T of this item has read Q_t
+//     (`q_free`), which is two blocks before the item ends;
+//   - the only wait the hand-over adds is O_t: the first PV of the next item starts when the
+//     epilogue has read O_t out of tensor memory (`o_free`).
+#pragma once
+
+namespace lf {
+
+constexpr int kItemSlots = 4;
+constexpr int kBoundedThreads = 21 * 32;  // 16 softmax + 1 producer + 2 PV + 2 QK warps
+constexpr uint32_t kBoundedStageBytes = 16 * 1024 + 2048;  // 16 x 1 KB output staging + row sums
+
+struct __align__(8) BoundedBarriers {
+  uint64_t q_full[2];
+  uint64_t q_free[2];      // [tile] last QK^T of the item has read Q_t
+  uint64_t kv_full[kMaxStages];
+  uint64_t kv_empty[kMaxStages];
+  uint64_t s_full[2][2];   // [tile][buffer]  MMA -> softmax
+  uint64_t p_full[2][2];   // [tile][buffer]  softmax -> MMA (one arrival per warp)
+  uint64_t pv_each[2][2];  // [tile][buffer]  PV of the block in that buffer done
+  uint64_t o_final[2];     // [tile] last PV of the item done
+  uint64_t o_free[2];      // [tile] epilogue has read O_t (one arrival per warp)
+  uint64_t l_ready[2];     // [tile] both halves of every row sum are published
+  uint64_t item_full[kItemSlots];   // producer -> everybody: item published
+  uint64_t item_empty[kItemSlots];  // 4 MMA threads + 16 softmax warps have read it
+  uint32_t tmem_base;
+  uint32_t pad;
+};
+
+// Geometry of one work item: decoded once by the producer and published through shared memory
+// (the divisions would otherwise be repeated by every softmax thread on the critical path).
+struct ItemGeom {
+  int32_t it;  // item id, -1 = queue empty
+  int32_t b, h, hkv, iq0;
+  int32_t lo0, hi0, lo1, hi1;  // KV block range of tile 0 / tile 1
+  int32_t flags;               // bit t: tile t lies inside Sq, bit 2 + t: tile t has work
+  int32_t lo, hi;              // union of the two ranges (what the K/V ring carries)
+  __device__ __forceinline__ bool valid(int t) const { return (flags >> t) & 1; }
+  __device__ __forceinline__ bool work(int t) const { return (flags >> (2 + t)) & 1; }
+  __device__ __forceinline__ int lo_t(int t) const { return t ? lo1 : lo0; }
+  __device__ __forceinline__ int hi_t(int t) const { return t ? hi1 : hi0; }
+};
+
+__device__ __forceinline__ ItemGeom decode_item(const PrefillParams& p, int it) {
+  ItemGeom g;
+  g.it = it;
+  const int pair = p.n_pairs - 1 - it % p.n_pairs;  // heaviest query tiles of a head first
+  const int hb = it / p.n_pairs;
+  g.h = hb % p.Hq;
+  g.b = hb / p.Hq;
+  g.hkv = g.h / p.group;
+  g.iq0 = pair * 2;
+  skip_range(p.mask_kind, p.window, p.causal_offset, p.Sq, p.Skv, kTileQ, kTileK, g.iq0, &g.lo0,
+             &g.hi0);
+  skip_range(p.mask_kind, p.window, p.causal_offset, p.Sq, p.Skv, kTileQ, kTileK, g.iq0 + 1,
+             &g.lo1, &g.hi1);
+  const bool v0 = g.iq0 * kTileQ < p.Sq, v1 = (g.iq0 + 1) * kTileQ < p.Sq;
+  const bool w0 = v0 && g.hi0 > g.lo0, w1 = v1 && g.hi1 > g.lo1;
+  g.flags = (v0 ? 1 : 0) | (v1 ? 2 : 0) | (w0 ? 4 : 0) | (w1 ? 8 : 0);
+  g.lo = 0;
+  g.hi = 0;
+  if (w0 && w1) {
+    g.lo = min(g.lo0, g.lo1);
+    g.hi = max(g.hi0, g.hi1);
+  } else if (w0) {
+    g.lo = g.lo0;
+    g.hi = g.hi0;
+  } else if (w1) {
+    g.lo = g.lo1;
+    g.hi = g.hi1;
+  }
+  return g;
+}
+
+template <int D>
+__global__ void __launch_bounds__(kBoundedThreads, 1)
+    prefill_bounded_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                           const __grid_constant__ CUtensorMap tmap_k,
+                           const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
+  constexpr int kStages = StagesFor<D>::value;
+  constexpr int kBlocksD = D / 64;
+  constexpr uint32_t kQBlockBytes = kTileQ * 128;
+  constexpr uint32_t kQTileBytes = kQBlockBytes * kBlocksD;
+  constexpr uint32_t kKVBlockBytes = kTileK * 128;
+  constexpr uint32_t kKVTileBytes = kKVBlockBytes * kBlocksD;
+  constexpr uint32_t kIdescQK = make_idesc_bf16(128, kTileK, 0);
+  constexpr uint32_t kIdescPV = make_idesc_bf16(128, D, 1);
+  constexpr uint32_t kColO = 256;
+  constexpr int kProducerWarp = 16;
+  constexpr int kMmaWarp0 = 17;
+
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~static_cast<uintptr_t>(1023));
+  BoundedBarriers* bars = reinterpret_cast<BoundedBarriers*>(smem);
+  static_assert(sizeof(BoundedBarriers) + 16 + kItemSlots * sizeof(ItemGeom) <= 1024, "barrier page");
+  static_assert(sizeof(ItemGeom) == 48, "three 16-byte pieces");
+  ItemGeom* item_slots =
+      reinterpret_cast<ItemGeom*>(smem + ((sizeof(BoundedBarriers) + 15) & ~size_t(15)));
+  unsigned char* sStage = smem + 1024;  // 16 x 1 KB output staging, then the row-sum slots
+  unsigned char* sQ = sStage + kBoundedStageBytes;
+  unsigned char* sKV = sQ + 2 * kQTileBytes;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---------------- setup ----------------
+  if (warp == kMmaWarp0 && lane == 0) {
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&bars->q_full[t], 1);
+      mbar_init(&bars->q_free[t], 1);
+      for (int bf = 0; bf < 2; ++bf) {
+        mbar_init(&bars->s_full[t][bf], 1);
+        mbar_init(&bars->p_full[t][bf], 8);
+        mbar_init(&bars->pv_each[t][bf], 1);
+      }
+      mbar_init(&bars->o_final[t], 1);
+      mbar_init(&bars->o_free[t], 8);
+      mbar_init(&bars->l_ready[t], 256);
+    }
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars->kv_full[s], 1);
+      mbar_init(&bars->kv_empty[s], 4);  // every MMA thread releases every stage
+    }
+    for (int s = 0; s < kItemSlots; ++s) {
+      mbar_init(&bars->item_full[s], 1);
+      mbar_init(&bars->item_empty[s], 20);
+    }
+    mbar_fence_init();
+  }
+  if (warp == kProducerWarp && lane == 0) {
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 0) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  // Next item of this role's sequence (it = -1: queue empty, or a wait ran out). Every consumer
+  // thread copies the slot itself; one arrival per MMA thread / softmax warp frees it.
+  auto next_item = [&](int seq, bool whole_warp) -> ItemGeom {
+    const int slot = seq % kItemSlots;
+    ItemGeom g;
+    if (!mbar_wait(&bars->item_full[slot], (seq / kItemSlots) & 1)) {
+      report_timeout(p.status, 20);
+      g.it = -1;
+      return g;
+    }
+    const int4* src = reinterpret_cast<const int4*>(&item_slots[slot]);
+    int4 v0 = src[0], v1 = src[1], v2 = src[2];
+    g.it = v0.x; g.b = v0.y; g.h = v0.z; g.hkv = v0.w;
+    g.iq0 = v1.x; g.lo0 = v1.y; g.hi0 = v1.z; g.lo1 = v1.w;
+    g.hi1 = v2.x; g.flags = v2.y; g.lo = v2.z; g.hi = v2.w;
+    if (whole_warp) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->item_empty[slot]);
+    } else {
+      mbar_arrive(&bars->item_empty[slot]);
+    }
+    return g;
+  };
+
+  if (warp == kProducerWarp) {
+    // ---------------- TMA producer (and item dispatcher) ----------------
+    if (lane == 0) {
+      LF_TRACE_DECL(3, true);
+      int n = 0;                // ring position, runs across items
+      int qseq[2] = {0, 0};     // items with work so far, per tile
+      bool ok = true;
+      auto load_pair = [&](const CUtensorMap* tma, int ja, int jb, int hkv, int b) {
+        if (!ok) return;
+        const int stage = n % kStages;
+        const uint32_t parity = ((n / kStages) & 1) ^ 1;
+        ++n;
+        LF_TRACE_EV(1);
+        if (!mbar_wait(&bars->kv_empty[stage], parity)) {
+          report_timeout(p.status, 1);
+          ok = false;
+          return;
+        }
+        LF_TRACE_EV(2);
+        mbar_arrive_expect_tx(&bars->kv_full[stage], jb >= 0 ? 2 * kKVTileBytes : kKVTileBytes);
+        unsigned char* dst = sKV + stage * (2 * kKVTileBytes);
+#pragma unroll
+        for (int kb = 0; kb < kBlocksD; ++kb)
+          tma_load_4d(dst + kb * kKVBlockBytes, tma, &bars->kv_full[stage], kb * 64, ja * kTileK,
+                      hkv, b);
+        if (jb >= 0) {
+#pragma unroll
+          for (int kb = 0; kb < kBlocksD; ++kb)
+            tma_load_4d(dst + kKVTileBytes + kb * kKVBlockBytes, &tmap_k, &bars->kv_full[stage],
+                        kb * 64, jb * kTileK, hkv, b);
+        }
+      };
+      for (int seq = 0; ok; ++seq) {
+        int it = static_cast<int>(atomicAdd(p.ticket, 1u));
+        if (it >= p.n_items) it = -1;
+        const int slot = seq % kItemSlots;
+        if (!mbar_wait(&bars->item_empty[slot], ((seq / kItemSlots) & 1) ^ 1)) {
+          report_timeout(p.status, 21);
+          break;
+        }
+        ItemGeom g;
+        if (it >= 0) g = decode_item(p, it);
+        else g.it = -1, g.b = g.h = g.hkv = g.iq0 = g.lo0 = g.hi0 = g.lo1 = g.hi1 = g.flags = g.lo = g.hi = 0;
+        item_slots[slot] = g;
+        mbar_arrive(&bars->item_full[slot]);  // release: the slot is visible to the waiters
+        if (it < 0) break;
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (!g.work(t)) continue;
+          // Q_t is free once the last QK^T of the previous item with work for this tile is done.
+          if (qseq[t] > 0 && !mbar_wait(&bars->q_free[t], (qseq[t] - 1) & 1)) {
+            report_timeout(p.status, 22);
+            ok = false;
+            break;
+          }
+          ++qseq[t];
+          mbar_arrive_expect_tx(&bars->q_full[t], kQTileBytes);
+#pragma unroll
+          for (int kb = 0; kb < kBlocksD; ++kb)
+            tma_load_4d(sQ + t * kQTileBytes + kb * kQBlockBytes, &tmap_q, &bars->q_full[t],
+                        kb * 64, (g.iq0 + t) * kTileQ, g.h, g.b);
+        }
+        if (g.hi > g.lo) {
+          load_pair(&tmap_k, g.lo, g.lo + 1 < g.hi ? g.lo + 1 : -1, g.hkv, g.b);
+          for (int j = g.lo; j < g.hi; ++j)
+            load_pair(&tmap_v, j, j + 2 < g.hi ? j + 2 : -1, g.hkv, g.b);
+        }
+      }
+      LF_TRACE_END();
+    }
+  } else if (warp >= kMmaWarp0 && warp < kMmaWarp0 + 4) {
+    // ---------------- MMA issuers: a PV thread and a QK^T thread per query tile ----------
+    // All four threads walk every ring stage and each releases it (kv_empty counts four
+    // arrivals) once the MMAs it issued from the stage, if any, are complete. A thread must see
+    // a stage full before it releases it: that keeps its arrivals one per phase.
+    if (lane == 0) {
+      const int t = (warp - kMmaWarp0) & 1;
+      const bool is_qk = warp - kMmaWarp0 >= 2;
+      bool ok = true;
+      LF_TRACE_DECL(2, t == 0 && is_qk);
+      LF_TRACE_EV(0);
+      constexpr uint32_t kStageUnits = (2 * kKVTileBytes) >> 4;  // a stage is a pair of tiles
+      constexpr uint32_t kHalfUnits = kKVTileBytes >> 4;
+      const uint32_t s_col = tmem_base + t * 128;
+      const uint32_t o_col = tmem_base + kColO + t * 128;
+      const uint64_t qdesc = make_smem_desc_sw128(smem_u32(sQ) + t * kQTileBytes, 16, 1024);
+      const uint64_t kdesc0 = make_smem_desc_sw128(smem_u32(sKV), 16, 1024);
+      const uint64_t vdesc0 = make_smem_desc_sw128(smem_u32(sKV), kKVBlockBytes, 1024);
+      int n = 0;     // ring position, runs across items
+      int gblk = 0;  // blocks of this tile so far (all items): buffer = gblk & 1
+      int wseq = 0;  // items with work for this tile so far
+      auto wait_stage = [&](int where) -> int {  // next ring stage, waited full; -1 on time-out
+        const int stage = n % kStages;
+        const uint32_t parity = (n / kStages) & 1;
+        ++n;
+        if (!mbar_wait(&bars->kv_full[stage], parity)) {
+          report_timeout(p.status, where);
+          ok = false;
+          return -1;
+        }
+        return stage;
+      };
+      for (int seq = 0; ok; ++seq) {
+        const ItemGeom g = next_item(seq, false);
+        if (g.it < 0) break;
+        if (g.hi <= g.lo) continue;
+        const int lo = g.lo, hi = g.hi, lo_tt = g.lo_t(t), hi_tt = g.hi_t(t);
+        const bool work = g.work(t);
+        auto active = [&](int j) { return work && j >= lo_tt && j < hi_tt; };
+        if (is_qk) {
+          if (work) {
+            if (!mbar_wait(&bars->q_full[t], wseq & 1)) {
+              report_timeout(p.status, 2);
+              ok = false;
+              break;
+            }
+            ++wseq;
+          }
+          // QK^T of block j of this item (global block number gj of the tile) from K tile
+          // `hf` of ring stage `stage`; its S buffer was last used by block gj - 2.
+          auto issue_qk = [&](int stage, int hf, int j) -> bool {
+            const int gj = gblk + (j - lo_tt);
+            const int buf = gj & 1;
+            if (gj >= 2 && !mbar_wait(&bars->pv_each[t][buf], ((gj - 2) >> 1) & 1)) {
+              report_timeout(p.status, 12 + t);
+              ok = false;
+              return false;
+            }
+            tc_fence_after();
+            const uint64_t kd =
+                kdesc0 + static_cast<uint64_t>(stage * kStageUnits + hf * kHalfUnits);
+            const uint32_t d = s_col + buf * 64;
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+              mma_ss(d,
+                     qdesc + static_cast<uint64_t>((ks / 4) * (kQBlockBytes >> 4) + (ks % 4) * 2),
+                     kd + static_cast<uint64_t>((ks / 4) * (kKVBlockBytes >> 4) + (ks % 4) * 2),
+                     kIdescQK, ks > 0 ? 1u : 0u);
+            }
+            tc_commit(&bars->s_full[t][buf]);
+            if (j == hi_tt - 1) tc_commit(&bars->q_free[t]);  // Q_t may be overwritten now
+            return true;
+          };
+          // First stage of the item: {K(lo), K(lo+1)}.
+          {
+            const int stage = wait_stage(3);
+            if (stage < 0) break;
+            tc_fence_after();
+            if (active(lo) && !issue_qk(stage, 0, lo)) break;
+            if (lo + 1 < hi && active(lo + 1) && !issue_qk(stage, 1, lo + 1)) break;
+            tc_commit(&bars->kv_empty[stage]);
+          }
+          for (int j = lo; j < hi && ok; ++j) {
+            LF_TRACE_EV(10);
+            const int st = wait_stage(4);  // {V(j), K(j+2)}
+            if (st < 0) break;
+            LF_TRACE_EV(11);
+            if (j + 2 < hi && active(j + 2)) {
+              tc_fence_after();
+              if (!issue_qk(st, 1, j + 2)) break;
+            }
+            tc_commit(&bars->kv_empty[st]);
+            LF_TRACE_EV(15);
+          }
+        } else {
+          {  // the first stage of an item holds K tiles only
+            const int st = wait_stage(5);
+            if (st < 0) break;
+            tc_commit(&bars->kv_empty[st]);
+          }
+          for (int j = lo; j < hi && ok; ++j) {
+            const int st = wait_stage(5);  // {V(j), K(j+2)}
+            if (st < 0) break;
+            if (active(j)) {
+              const int kt = j - lo_tt;
+              const int gj = gblk + kt;
+              // O_t of the previous item must have been read out before it is overwritten.
+              if (kt == 0 && wseq > 0 && !mbar_wait(&bars->o_free[t], (wseq - 1) & 1)) {
+                report_timeout(p.status, 14 + t);
+                ok = false;
+                break;
+              }
+              if (!mbar_wait(&bars->p_full[t][gj & 1], (gj >> 1) & 1)) {
+                report_timeout(p.status, 6 + t);
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+              const uint64_t vd = vdesc0 + static_cast<uint64_t>(st * kStageUnits);
+              const uint32_t a = s_col + (gj & 1) * 64;
+#pragma unroll
+              for (int ks = 0; ks < kTileK / 16; ++ks) {
+                // P columns of 16 keys: 16 columns at the start of each 32-column half of S.
+                mma_ts(o_col, a + (ks >> 1) * 32 + (ks & 1) * 8,
+                       vd + static_cast<uint64_t>(ks * (2048 >> 4)), kIdescPV,
+                       (kt > 0 || ks > 0) ? 1u : 0u);
+              }
+              tc_commit(&bars->pv_each[t][gj & 1]);
+              if (j == hi_tt - 1) tc_commit(&bars->o_final[t]);
+            }
+            tc_commit(&bars->kv_empty[st]);
+          }
+          if (work) ++wseq;
+        }
+        if (work) gblk += hi_tt - lo_tt;
+      }
+      LF_TRACE_END();
+    }
+  } else {
+    // ---------------- softmax warps ----------------
+    // Query tile t = warpgroup / 2; inside a tile, warpgroup `half` takes columns
+    // [32*half, 32*half + 32) of every 64-key block, one thread per (row, half). With the fixed
+    // reference there is no running max, no rescale of O and nothing to exchange between the
+    // two threads of a row until the final row sum.
+    const int wg = warp >> 2;
+    const int t = wg >> 1;
+    const int half = wg & 1;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;  // row inside the tile == tensor-memory lane
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_base = tmem_base + lane_addr + t * 128 + half * 32;
+    const uint32_t o_addr = tmem_base + lane_addr + kColO + t * 128;
+    unsigned char* stage = sStage + warp * 1024;
+    float* l_slots = reinterpret_cast<float*>(sStage + 16 * 1024) + t * 256;  // [half][row]
+    // tanh(x) = x*(1 + y*(-1/3 + y*(2/15 + y*(-17/315)))), y = x^2, x = a*raw. The powers of a and
+    // the output factor c2 are folded into the coefficients p.qc[] on the host, so the polynomial
+    // runs on raw^2 and gives logit2 = raw * q(raw^2) directly; p.ylim[] are the limits of the two
+    // polynomials as bounds on raw^2.
+    const uint64_t q0c = pack2(p.qc[0], p.qc[0]);
+    const uint64_t q1c = pack2(p.qc[1], p.qc[1]);
+    // The tanh evaluation (0: degree 3, 1: degree 7, 2: MUFU) is chosen speculatively: a block
+    // starts with what the warp's previous block needed, and is redone on the spot with a
+    // stronger one if its own max |x| (known after the pass) asks for it.
+    int path = 0;
+    int gblk = 0;  // blocks of this tile so far (all items): buffer = gblk & 1
+    int wseq = 0;  // items with work for this tile so far
+    bool ok = true;
+    LF_TRACE_DECL(t, half == 0 && quarter == 0 && lane == 0);
+    for (int seq = 0; ok; ++seq) {
+      const ItemGeom g = next_item(seq, true);
+      LF_TRACE_EV(28);
+      if (g.it < 0) break;
+      const int grow = (g.iq0 + t) * kTileQ + row;
+#ifndef LF_TRACE
+      if (p.dbg_ranges && g.valid(t) && row == 0 && half == 0) {
+        const int64_t idx =
+            ((static_cast<int64_t>(g.b) * p.Hq + g.h) * p.n_qtiles + (g.iq0 + t)) * 2;
+        p.dbg_ranges[idx] = g.lo_t(t);
+        p.dbg_ranges[idx + 1] = g.hi_t(t);
+      }
+#endif
+      if (!g.work(t)) {
+        if (g.valid(t) && grow < p.Sq && half == 0) {
+          // No visible key at all for this tile: softmax of an all -inf row is NaN in the
+          // eager computation, so the rows are written as NaN.
+          __nv_bfloat16* orow = p.out + g.b * p.o_stride[0] + g.h * p.o_stride[1] +
+                                static_cast<int64_t>(grow) * p.o_stride[2];
+          const uint4 nan4 = {0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u};
+#pragma unroll
+          for (int c = 0; c < D; c += 8) *reinterpret_cast<uint4*>(orow + c) = nan4;
+        }
+        continue;
+      }
+      // Visible column interval of this row: [c_lo, c_hi].
+      int c_hi = p.Skv - 1;
+      int c_lo = 0;
+      if (p.mask_kind != LF_MASK_NONE) c_hi = min(c_hi, grow + p.causal_offset);
+      if (p.mask_kind == LF_MASK_CAUSAL_WINDOW)
+        c_lo = max(0, grow + p.causal_offset - (p.window - 1));
+
+      float l_run = 0.f;
+      const int lo_tt = g.lo_t(t);
+      const int nblk = g.hi_t(t) - lo_tt;
+      for (int k = 0; k < nblk; ++k) {
+        const int c0 = (lo_tt + k) * kTileK + half * 32;  // first key column of this thread
+        const int gk = gblk + k;
+        const int buf = gk & 1;
+        const uint32_t s_addr = s_base + buf * 64;
+        LF_TRACE_EV(20);
+        if (!mbar_wait(&bars->s_full[t][buf], (gk >> 1) & 1)) {
+          report_timeout(p.status, 8 + t);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        LF_TRACE_EV(21);
+        const int rel_lo = c_lo - c0;  // visible columns of this thread's 32: [rel_lo, rel_hi]
+        const int rel_hi = c_hi - c0;
+        const bool masked = rel_lo > 0 || rel_hi < 31;
+
+        uint32_t pk[16];
+        float block_sum = 0.f;
+        for (;;) {
+          // (Read again from tensor memory when a block is redone: P is stored only at the end.)
+          uint32_t sr[32];
+          tmem_ld_32x32b_x32(s_addr, sr);
+          tmem_wait_ld();
+          LF_TRACE_EV(22);
+          float psum[4] = {0.f, 0.f, 0.f, 0.f};
+          float ymax0 = 0.f, ymax1 = 0.f;
+          auto finish_pair = [&](uint64_t z2, int i, bool apply_mask) {
+            float z0, z1;
+            unpack2(z2, z0, z1);
+            if (apply_mask) {
+              if (i < rel_lo || i > rel_hi) z0 = -INFINITY;
+              if (i + 1 < rel_lo || i + 1 > rel_hi) z1 = -INFINITY;
+            }
+            // Every exponential goes to MUFU: this loop is bound by instruction dispatch, and two
+            // ex2 cost less of it than an FMA-pipe emulation would.
+            const uint32_t pkv = pack_bf16x2(ex2_approx(z0), ex2_approx(z1));
+            pk[i >> 1] = pkv;
+            // The row sum is taken over the bf16-rounded values that the PV product sees, so that
+            // numerator and denominator carry the same rounding (the largest P of a row is not
+            // exactly 1 as it would be with a running max). The mixed-precision add reads the
+            // bf16 halves directly.
+            if ((i >> 1) & 1) add_bf16x2_to_f32(psum[2], psum[3], pkv);
+            else add_bf16x2_to_f32(psum[0], psum[1], pkv);
+          };
+          auto body = [&](auto path_tag, bool apply_mask) {
+            constexpr int kPath = decltype(path_tag)::value;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const uint64_t r2 = pack2u(sr[i], sr[i + 1]);
+              const uint64_t y2 = mul2(r2, r2);
+              float y0, y1;
+              unpack2(y2, y0, y1);
+              if ((i >> 1) & 1) ymax1 = max3(ymax1, y0, y1); else ymax0 = max3(ymax0, y0, y1);
+              uint64_t z2;
+              if constexpr (kPath == 0) {
+                z2 = mul2(r2, fma2(y2, q1c, q0c));
+              } else if constexpr (kPath == 1) {
+                uint64_t q2 = fma2(y2, pack2(p.qc[3], p.qc[3]), pack2(p.qc[2], p.qc[2]));
+                q2 = fma2(q2, y2, q1c);
+                q2 = fma2(q2, y2, q0c);
+                z2 = mul2(r2, q2);
+              } else {
+                const float t0 = tanh_approx(__uint_as_float(sr[i]) * p.a);
+                const float t1 = tanh_approx(__uint_as_float(sr[i + 1]) * p.a);
+                z2 = mul2(pack2(t0, t1), pack2(p.c2, p.c2));
+              }
+              finish_pair(z2, i, apply_mask);
+            }
+          };
+          if (path == 0) {
+            if (masked) body(std::integral_constant<int, 0>{}, true);
+            else body(std::integral_constant<int, 0>{}, false);
+          } else if (path == 1) {
+            if (masked) body(std::integral_constant<int, 1>{}, true);
+            else body(std::integral_constant<int, 1>{}, false);
+          } else {
+            if (masked) body(std::integral_constant<int, 2>{}, true);
+            else body(std::integral_constant<int, 2>{}, false);
+          }
+          block_sum = (psum[0] + psum[1]) + (psum[2] + psum[3]);
+          // What this block needed, over the whole warp (masked columns included: their raw
+          // scores are ordinary finite numbers).
+          const float ymax = fmaxf(ymax0, ymax1);
+          const unsigned mine = ymax > p.ylim[1] ? 2u : (ymax > p.ylim[0] ? 1u : 0u);
+          const int needed = static_cast<int>(__reduce_max_sync(0xffffffffu, mine));
+          const bool redo = needed > path;
+          path = needed;
+          if (!redo) break;
+        }
+        l_run += block_sum;
+        LF_TRACE_EV(24);
+        // P (bf16, two per column) goes on top of the first 16 of this thread's S columns.
+        tmem_st_32x32b_x16(s_addr, pk);
+        tmem_wait_st();
+        tc_fence_before();
+        // One arrival per warp (256 arrivals on one barrier word would serialise).
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->p_full[t][buf]);
+        LF_TRACE_EV(25);
+      }
+      if (!ok) break;
+      gblk += nblk;
+      LF_TRACE_EV(26);
+
+      // Row sum: the two halves meet in shared memory.
+      l_slots[half * 128 + row] = l_run;
+      mbar_arrive(&bars->l_ready[t]);
+      if (!mbar_wait(&bars->l_ready[t], wseq & 1)) {
+        report_timeout(p.status, 18 + t);
+        ok = false;
+        break;
+      }
+      l_run = l_slots[row] + l_slots[128 + row];
+      LF_TRACE_EV(30);
+      // Epilogue: O_t / l -> bf16 -> global; each half writes D/2 of the row's columns.
+      if (!mbar_wait(&bars->o_final[t], wseq & 1)) {
+        report_timeout(p.status, 10 + t);
+        ok = false;
+        break;
+      }
+      ++wseq;
+      tc_fence_after();
+      LF_TRACE_EV(31);
+      const float inv = 1.f / l_run;
+      __nv_bfloat16* obase = p.out + g.b * p.o_stride[0] + g.h * p.o_stride[1];
+      const int row0 = (g.iq0 + t) * kTileQ + quarter * 32;  // first global row of the warp
+      uint32_t orr[D / 64][32];
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) tmem_ld_32x32b_x32(o_addr + half * (D / 2) + c * 32, orr[c]);
+      tmem_wait_ld();
+      // O_t is in registers: the first PV of the next item may overwrite it.
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->o_free[t]);
+      LF_TRACE_EV(32);
+#ifdef LF_EPI_DIRECT
+      // One thread holds 64 consecutive columns of its row: 128 contiguous bytes.
+      if (grow < p.Sq) {
+        __nv_bfloat16* orow = obase + static_cast<int64_t>(grow) * p.o_stride[2] + half * (D / 2);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t* src = &orr[c][q * 8];
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(src[0]) * inv, __uint_as_float(src[1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(src[2]) * inv, __uint_as_float(src[3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(src[4]) * inv, __uint_as_float(src[5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(src[6]) * inv, __uint_as_float(src[7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = w;
+          }
+        }
+      }
+      (void)stage; (void)row0;
+#else
+      // Each warp owns 32 rows; 16 columns at a time (32 bytes per row) go through a swizzled
+      // 1 KB buffer of the warp so that one store instruction writes sixteen 32-byte row
+      // segments instead of thirty-two 16-byte pieces.
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+#pragma unroll
+        for (int hq = 0; hq < 2; ++hq) {
+          const int col = half * (D / 2) + c * 32 + hq * 16;
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {  // piece q of row r sits at position q ^ ((r >> 2) & 1)
+            const uint32_t* src = &orr[c][hq * 16 + q * 8];
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(src[0]) * inv, __uint_as_float(src[1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(src[2]) * inv, __uint_as_float(src[3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(src[4]) * inv, __uint_as_float(src[5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(src[6]) * inv, __uint_as_float(src[7]) * inv);
+            *reinterpret_cast<uint4*>(stage + lane * 32 + ((q ^ ((lane >> 2) & 1)) << 4)) = w;
+          }
+          __syncwarp();
+#pragma unroll
+          for (int rr = 0; rr < 2; ++rr) {
+            const int r = rr * 16 + (lane >> 1);
+            const int q = lane & 1;
+            const uint4 w =
+                *reinterpret_cast<const uint4*>(stage + r * 32 + ((q ^ ((r >> 2) & 1)) << 4));
+            if (row0 + r < p.Sq)
+              *reinterpret_cast<uint4*>(obase + static_cast<int64_t>(row0 + r) * p.o_stride[2] +
+                                        col + q * 8) = w;
+          }
+          __syncwarp();
+        }
+      }
+#endif
+      LF_TRACE_EV(27);
+    }
+    LF_TRACE_END();
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace lf
