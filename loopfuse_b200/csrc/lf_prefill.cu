@@ -1080,10 +1080,12 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
   return fn;
 }
 
-// Tensor map over a bf16 [B, H, S, D] tensor (innermost stride 1), box = [1, 1, box_rows, 64],
-// 128-byte swizzle, out-of-range rows read as zero.
+// Tensor map over a bf16 [B, H, S, D] tensor (innermost stride 1), box = [1, 1, box_rows,
+// box_cols]; 128-byte swizzle for 64-column boxes (the K/V/Q loads, out-of-range rows read as
+// zero), 64-byte swizzle for 32-column boxes (the output store of the persistent kernel).
 static int make_tile_map(CUtensorMap* map, const void* base, int B, int H, int S, int D,
-                         const int64_t* stride /* b, h, s in elements */, int box_rows) {
+                         const int64_t* stride /* b, h, s in elements */, int box_rows,
+                         int box_cols = 64) {
   auto fn = get_encode_fn();
   if (!fn) return LF_ERR_CUDA;
   cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S),
@@ -1099,10 +1101,11 @@ static int make_tile_map(CUtensorMap* map, const void* base, int B, int H, int S
       else
         return LF_ERR_ALIGNMENT;
     }
-  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
+  cuuint32_t box[4] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows), 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims,
-                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
@@ -1146,7 +1149,8 @@ static __device__ unsigned int g_prefill_tickets[kTicketSlots];
 
 template <int D>
 static int launch_prefill_bounded(const CUtensorMap& mq, const CUtensorMap& mk,
-                                  const CUtensorMap& mv, PrefillParams p, int B, cudaStream_t st) {
+                                  const CUtensorMap& mv, const CUtensorMap& mo, PrefillParams p,
+                                  int B, cudaStream_t st) {
   constexpr size_t kQTileBytes = static_cast<size_t>(kTileQ) * D * 2;
   constexpr size_t kKVTileBytes = static_cast<size_t>(kTileK) * D * 2;
   constexpr size_t smem = 1024 /*align slack*/ + 1024 /*barriers*/ + kBoundedStageBytes +
@@ -1181,7 +1185,7 @@ static int launch_prefill_bounded(const CUtensorMap& mq, const CUtensorMap& mk,
     return LF_ERR_CUDA;
   }
   const int grid = static_cast<int>(n_items < sm_count ? n_items : sm_count);
-  prefill_bounded_kernel<D><<<grid, kBoundedThreads, smem, st>>>(mq, mk, mv, p);
+  prefill_bounded_kernel<D><<<grid, kBoundedThreads, smem, st>>>(mq, mk, mv, mo, p);
   return check_launch("prefill_bounded_kernel");
 }
 
@@ -1283,12 +1287,18 @@ static int prefill_impl(const LfPrefillArgs* a, void* stream) {
   rc = make_tile_map(&mv, a->v, a->B, a->Hkv, a->Skv, a->D, a->v_stride, kTileK);
   if (rc != LF_OK) return rc;
 
+  CUtensorMap mo;  // output store boxes of the persistent kernel: 32 rows x 32 columns
+  if (mode == kModeBounded) {
+    rc = make_tile_map(&mo, a->out, a->B, a->Hq, a->Sq, a->D, a->o_stride, 32, 32);
+    if (rc != LF_OK) return rc;
+  }
+
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (a->D == 128) {
     if (mode == kModeNone) return launch_prefill<128, kModeNone>(mq, mk, mv, p, a->B, st);
     if (mode == kModeSoftcap) return launch_prefill<128, kModeSoftcap>(mq, mk, mv, p, a->B, st);
 #ifndef LF_NO_PERSISTENT
-    if (mode == kModeBounded) return launch_prefill_bounded<128>(mq, mk, mv, p, a->B, st);
+    if (mode == kModeBounded) return launch_prefill_bounded<128>(mq, mk, mv, mo, p, a->B, st);
 #endif
     if (mode == kModeBounded) return launch_prefill<128, kModeBounded>(mq, mk, mv, p, a->B, st);
     return launch_prefill<128, kModeGeneric>(mq, mk, mv, p, a->B, st);
@@ -1296,7 +1306,7 @@ static int prefill_impl(const LfPrefillArgs* a, void* stream) {
   if (mode == kModeNone) return launch_prefill<64, kModeNone>(mq, mk, mv, p, a->B, st);
   if (mode == kModeSoftcap) return launch_prefill<64, kModeSoftcap>(mq, mk, mv, p, a->B, st);
 #ifndef LF_NO_PERSISTENT
-  if (mode == kModeBounded) return launch_prefill_bounded<64>(mq, mk, mv, p, a->B, st);
+  if (mode == kModeBounded) return launch_prefill_bounded<64>(mq, mk, mv, mo, p, a->B, st);
 #endif
   if (mode == kModeBounded) return launch_prefill<64, kModeBounded>(mq, mk, mv, p, a->B, st);
   return launch_prefill<64, kModeGeneric>(mq, mk, mv, p, a->B, st);

@@ -19,7 +19,7 @@ namespace lf {
 
 constexpr int kItemSlots = 4;
 constexpr int kBoundedThreads = 21 * 32;  // 16 softmax + 1 producer + 2 PV + 2 QK warps
-constexpr uint32_t kBoundedStageBytes = 16 * 1024 + 2048;  // 16 x 1 KB output staging + row sums
+constexpr uint32_t kBoundedStageBytes = 16 * 2048;  // 2 KB of output staging per softmax warp
 
 struct __align__(8) BoundedBarriers {
   uint64_t q_full[2];
@@ -87,7 +87,8 @@ template <int D>
 __global__ void __launch_bounds__(kBoundedThreads, 1)
     prefill_bounded_kernel(const __grid_constant__ CUtensorMap tmap_q,
                            const __grid_constant__ CUtensorMap tmap_k,
-                           const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
+                           const __grid_constant__ CUtensorMap tmap_v,
+                           const __grid_constant__ CUtensorMap tmap_o, const PrefillParams p) {
   constexpr int kStages = StagesFor<D>::value;
   constexpr int kBlocksD = D / 64;
   constexpr uint32_t kQBlockBytes = kTileQ * 128;
@@ -108,7 +109,7 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
   static_assert(sizeof(ItemGeom) == 48, "three 16-byte pieces");
   ItemGeom* item_slots =
       reinterpret_cast<ItemGeom*>(smem + ((sizeof(BoundedBarriers) + 15) & ~size_t(15)));
-  unsigned char* sStage = smem + 1024;  // 16 x 1 KB output staging, then the row-sum slots
+  unsigned char* sStage = smem + 1024;  // 16 x 2 KB output staging (one buffer per softmax warp)
   unsigned char* sQ = sStage + kBoundedStageBytes;
   unsigned char* sKV = sQ + 2 * kQTileBytes;
 
@@ -143,6 +144,7 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
+    tma_prefetch_desc(&tmap_o);
   }
   if (warp == 0) {
     tmem_alloc(&bars->tmem_base, 512);
@@ -398,8 +400,11 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t s_base = tmem_base + lane_addr + t * 128 + half * 32;
     const uint32_t o_addr = tmem_base + lane_addr + kColO + t * 128;
-    unsigned char* stage = sStage + warp * 1024;
-    float* l_slots = reinterpret_cast<float*>(sStage + 16 * 1024) + t * 256;  // [half][row]
+    // Output staging of this warp; the warp that holds the other half of the same rows is
+    // warp ^ 4. The two exchange their row sums through the start of each other's buffer.
+    unsigned char* stage = sStage + warp * 2048;
+    float* l_mine = reinterpret_cast<float*>(stage) + lane;
+    float* l_partner = reinterpret_cast<float*>(sStage + (warp ^ 4) * 2048) + lane;
     // tanh(x) = x*(1 + y*(-1/3 + y*(2/15 + y*(-17/315)))), y = x^2, x = a*raw. The powers of a and
     // the output factor c2 are folded into the coefficients p.qc[] on the host, so the polynomial
     // runs on raw^2 and gives logit2 = raw * q(raw^2) directly; p.ylim[] are the limits of the two
@@ -413,6 +418,7 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
     int gblk = 0;  // blocks of this tile so far (all items): buffer = gblk & 1
     int wseq = 0;  // items with work for this tile so far
     bool ok = true;
+    bool store_pending = false;  // an output store of this warp may still be reading `stage`
     LF_TRACE_DECL(t, half == 0 && quarter == 0 && lane == 0);
     for (int seq = 0; ok; ++seq) {
       const ItemGeom g = next_item(seq, true);
@@ -545,6 +551,10 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
         tmem_st_32x32b_x16(s_addr, pk);
         tmem_wait_st();
         tc_fence_before();
+        if (store_pending) {  // (see the epilogue) long complete by now: no real wait
+          if (lane == 0) tma_store_wait_read();
+          store_pending = false;
+        }
         // One arrival per warp (256 arrivals on one barrier word would serialise).
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->p_full[t][buf]);
@@ -554,15 +564,17 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
       gblk += nblk;
       LF_TRACE_EV(26);
 
-      // Row sum: the two halves meet in shared memory.
-      l_slots[half * 128 + row] = l_run;
+      // Row sum: each thread leaves its half in the partner's staging buffer. (The partner's
+      // bulk store of the previous item has read that buffer: the partner checked it before its
+      // first P of this item, which every block of this item needed.)
+      *l_partner = l_run;
       mbar_arrive(&bars->l_ready[t]);
       if (!mbar_wait(&bars->l_ready[t], wseq & 1)) {
         report_timeout(p.status, 18 + t);
         ok = false;
         break;
       }
-      l_run = l_slots[row] + l_slots[128 + row];
+      l_run += *l_mine;
       LF_TRACE_EV(30);
       // Epilogue: O_t / l -> bf16 -> global; each half writes D/2 of the row's columns.
       if (!mbar_wait(&bars->o_final[t], wseq & 1)) {
@@ -574,7 +586,6 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
       tc_fence_after();
       LF_TRACE_EV(31);
       const float inv = 1.f / l_run;
-      __nv_bfloat16* obase = p.out + g.b * p.o_stride[0] + g.h * p.o_stride[1];
       const int row0 = (g.iq0 + t) * kTileQ + quarter * 32;  // first global row of the warp
       uint32_t orr[D / 64][32];
 #pragma unroll
@@ -585,61 +596,40 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->o_free[t]);
       LF_TRACE_EV(32);
-#ifdef LF_EPI_DIRECT
-      // One thread holds 64 consecutive columns of its row: 128 contiguous bytes.
-      if (grow < p.Sq) {
-        __nv_bfloat16* orow = obase + static_cast<int64_t>(grow) * p.o_stride[2] + half * (D / 2);
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const uint32_t* src = &orr[c][q * 8];
-            uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(src[0]) * inv, __uint_as_float(src[1]) * inv);
-            w.y = pack_bf16x2(__uint_as_float(src[2]) * inv, __uint_as_float(src[3]) * inv);
-            w.z = pack_bf16x2(__uint_as_float(src[4]) * inv, __uint_as_float(src[5]) * inv);
-            w.w = pack_bf16x2(__uint_as_float(src[6]) * inv, __uint_as_float(src[7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = w;
-          }
-        }
-      }
-      (void)stage; (void)row0;
-#else
-      // Each warp owns 32 rows; 16 columns at a time (32 bytes per row) go through a swizzled
-      // 1 KB buffer of the warp so that one store instruction writes sixteen 32-byte row
-      // segments instead of thirty-two 16-byte pieces.
+      // The warp's 32 rows x 32 columns go to its staging buffer in the 64-byte swizzle of the
+      // output tensor map (16-byte piece q of row r at position q ^ ((r >> 1) & 3), conflict
+      // free), and one bulk tensor store moves them to global memory; rows past Sq are clipped
+      // by the hardware. The store engine, not the load/store unit of the SM, writes the
+      // 32 x 64-byte row segments.
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
-#pragma unroll
-        for (int hq = 0; hq < 2; ++hq) {
-          const int col = half * (D / 2) + c * 32 + hq * 16;
-#pragma unroll
-          for (int q = 0; q < 2; ++q) {  // piece q of row r sits at position q ^ ((r >> 2) & 1)
-            const uint32_t* src = &orr[c][hq * 16 + q * 8];
-            uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(src[0]) * inv, __uint_as_float(src[1]) * inv);
-            w.y = pack_bf16x2(__uint_as_float(src[2]) * inv, __uint_as_float(src[3]) * inv);
-            w.z = pack_bf16x2(__uint_as_float(src[4]) * inv, __uint_as_float(src[5]) * inv);
-            w.w = pack_bf16x2(__uint_as_float(src[6]) * inv, __uint_as_float(src[7]) * inv);
-            *reinterpret_cast<uint4*>(stage + lane * 32 + ((q ^ ((lane >> 2) & 1)) << 4)) = w;
-          }
-          __syncwarp();
-#pragma unroll
-          for (int rr = 0; rr < 2; ++rr) {
-            const int r = rr * 16 + (lane >> 1);
-            const int q = lane & 1;
-            const uint4 w =
-                *reinterpret_cast<const uint4*>(stage + r * 32 + ((q ^ ((r >> 2) & 1)) << 4));
-            if (row0 + r < p.Sq)
-              *reinterpret_cast<uint4*>(obase + static_cast<int64_t>(row0 + r) * p.o_stride[2] +
-                                        col + q * 8) = w;
-          }
+        if (c > 0) {  // the previous box must have been read before the buffer is refilled
+          if (lane == 0) tma_store_wait_read();
           __syncwarp();
         }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t* src = &orr[c][q * 8];
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(src[0]) * inv, __uint_as_float(src[1]) * inv);
+          w.y = pack_bf16x2(__uint_as_float(src[2]) * inv, __uint_as_float(src[3]) * inv);
+          w.z = pack_bf16x2(__uint_as_float(src[4]) * inv, __uint_as_float(src[5]) * inv);
+          w.w = pack_bf16x2(__uint_as_float(src[6]) * inv, __uint_as_float(src[7]) * inv);
+          *reinterpret_cast<uint4*>(stage + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) = w;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_4d(&tmap_o, stage, half * (D / 2) + c * 32, row0, g.h, g.b);
+          tma_store_commit();
+        }
       }
-#endif
+      // The buffer is written again (by the partner, with its row sum) at the end of the next
+      // item; this warp confirms that the store has read it before its first P of that item.
+      store_pending = true;
       LF_TRACE_EV(27);
     }
+    if (lane == 0) tma_store_wait_all();  // all output stores of this warp are complete
     LF_TRACE_END();
   }
 
