@@ -1,32 +1,31 @@
 // Prefill attention for sm_100a: TMA-staged tiles, tcgen05 MMA with accumulators in tensor
-// memory, online softmax in registers.
+// memory, online softmax in registers. Two kernels share the tile shapes, the shared-memory
+// and tensor-memory layouts and the host code of this file:
 //
-// One CTA owns two consecutive 128-row query tiles of one (batch, q head) and walks the 64-key
-// KV tiles that the skip range leaves (fully masked tiles are never loaded or multiplied).
+//   prefill_kernel<D, MODE> (this file): the running-max modes - plain scores, generic score
+//       mods, softcap with a large cap. One CTA per pair of query tiles.
+//   prefill_bounded_kernel<D> (lf_prefill_bounded.cuh): softcap whose output range needs no
+//       running max (the benchmark configurations). Persistent, one CTA per SM.
 //
-// Running-max modes (plain scores, generic score mods, softcap with a large cap), 352 threads:
+// prefill_kernel: one CTA owns two consecutive 128-row query tiles of one (batch, q head) and
+// walks the 64-key KV tiles that the skip range leaves (fully masked tiles are never loaded or
+// multiplied). 352 threads:
 //   warps 0-3   softmax for query tile 0 (one thread per score row)
 //   warps 4-7   softmax for query tile 1
 //   warp  8     TMA producer: Q tiles once, then pairs of K/V tiles into a ring, in the order
 //               the MMA warps consume them: {K(lo), K(lo+1)}, {V(lo), K(lo+2)}, {V(lo+1), ...
 //   warp  9/10  MMA issuers (one thread each, one per query tile): S_t[buf] = Q_t K^T,
 //               O_t += P_t V
-// Bounded-score mode (softcap whose output range needs no running max), 672 threads:
-//   warps 0-7   softmax for query tile 0: two threads per score row, 32 columns of a block each
-//   warps 8-15  softmax for query tile 1
-//   warp  16    TMA producer (same ring)
-//   warps 17/18 PV issuers of tile 0 / 1, warps 19/20 QK^T issuers of tile 0 / 1
 //
 // Tensor memory (512 columns x 128 lanes of 32 bit):
 //   tile t, buffer b: S at column t*128 + b*64 (64 fp32 columns); P (bf16, two per column)
-//   overwrites the first 32 columns of its S buffer (bounded mode: the first 16 columns of each
-//   32-column half).   O_t at column 256 + t*128 (D columns).
+//   overwrites the first 32 columns of its S buffer.   O_t at column 256 + t*128 (D columns).
 //
 // S is double-buffered per query tile: QK^T of KV tile j+2 is issued right after PV of tile j,
 // so the tensor pipe computes the next scores while the softmax warps work on the current
-// ones; the only dependency left between the two sides is "PV(j) needs P(j)". In the
-// running-max modes the softmax warps rescale O_t in place when the max moves by more than 2^8
-// (rare); "S(k+1) is ready" tells them that PV(k-1) is complete.
+// ones; the only dependency left between the two sides is "PV(j) needs P(j)". The softmax warps
+// rescale O_t in place when the running max moves by more than 2^8 (rare); "S(k+1) is ready"
+// tells them that PV(k-1) is complete.
 //
 // Shared-memory tiles use the 128-byte swizzle that TMA writes and the MMA descriptors read:
 // a [rows][D] bf16 tile is stored as D/64 blocks of [rows][64] (128-byte rows).
@@ -48,9 +47,7 @@ namespace lf {
 constexpr int kTileQ = LF_PREFILL_TILE_Q;
 constexpr int kTileK = LF_PREFILL_TILE_K;
 static_assert(kTileQ == 128 && kTileK == 64, "the kernel is written for 128 x 64 tiles");
-// Threads per CTA: the softmax warps, one producer warp and the MMA-issuer warps (8 + 1 + 2, or
-// 16 + 1 + 4 in the bounded-score mode).
-constexpr int prefill_threads(int mode) { return mode == 3 ? 21 * 32 : 11 * 32; }
+constexpr int kPrefillThreads = 11 * 32;  // 8 softmax warps, 1 producer warp, 2 MMA-issuer warps
 constexpr int kMaxStages = 16;
 constexpr uint32_t kStageBytesTotal = 8 * 2048;
 // K/V ring depth in stages of two 64-key tiles: 4 x 32 KB at D=128, 8 x 16 KB at D=64 (which
@@ -106,9 +103,7 @@ struct __align__(8) PrefillBarriers {
   uint64_t s_full[2][2];   // [tile][buffer]  MMA -> softmax
   uint64_t p_full[2][2];   // [tile][buffer]  softmax -> MMA
   uint64_t pv_done[2];     // [tile] second-to-last PV done (running-max modes)
-  uint64_t pv_each[2][2];  // [tile][buffer] bounded mode: PV of the block in that buffer done
   uint64_t o_final[2];     // [tile] last PV done
-  uint64_t l_ready[2];     // [tile] bounded mode: both halves of every row sum are published
   uint32_t tmem_base;
   uint32_t pad;
 };
@@ -143,13 +138,10 @@ struct Tracer {
 
 __device__ __forceinline__ void report_timeout(int32_t* status, int where) {
   if (status) atomicCAS(status, LF_DEV_OK, LF_DEV_TIMEOUT | (where << 8));
-#ifdef LF_DIAG_SITES
-  if (status) atomicOr(status + 1, 1 << where);
-#endif
 }
 
 template <int D, int MODE>
-__global__ void __launch_bounds__(prefill_threads(MODE), 1)
+__global__ void __launch_bounds__(kPrefillThreads, 1)
     prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
                    const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
@@ -162,8 +154,7 @@ __global__ void __launch_bounds__(prefill_threads(MODE), 1)
   constexpr uint32_t kIdescQK = make_idesc_bf16(128, kTileK, 0);
   constexpr uint32_t kIdescPV = make_idesc_bf16(128, D, 1);
   constexpr uint32_t kColO = 256;
-  constexpr bool kSplit = MODE == kModeBounded;  // two threads per score row
-  constexpr int kSoftmaxWarps = kSplit ? 16 : 8;
+  constexpr int kSoftmaxWarps = 8;
   constexpr int kProducerWarp = kSoftmaxWarps;
   constexpr int kMmaWarp0 = kSoftmaxWarps + 1;
 
@@ -210,18 +201,15 @@ __global__ void __launch_bounds__(prefill_threads(MODE), 1)
     mbar_init(&bars->q_full[1], 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&bars->kv_full[s], 1);
-      mbar_init(&bars->kv_empty[s], kSplit ? 4 : 2);  // one arrival per MMA thread
+      mbar_init(&bars->kv_empty[s], 2);
     }
     for (int t = 0; t < 2; ++t) {
       for (int bf = 0; bf < 2; ++bf) {
         mbar_init(&bars->s_full[t][bf], 1);
-        mbar_init(&bars->p_full[t][bf], kSplit ? 8 : 128);  // split: one arrival per warp
+        mbar_init(&bars->p_full[t][bf], 128);
       }
       mbar_init(&bars->pv_done[t], 1);
-      mbar_init(&bars->pv_each[t][0], 1);
-      mbar_init(&bars->pv_each[t][1], 1);
       mbar_init(&bars->o_final[t], 1);
-      mbar_init(&bars->l_ready[t], 256);
     }
     mbar_fence_init();
   }
@@ -287,124 +275,7 @@ __global__ void __launch_bounds__(prefill_threads(MODE), 1)
       }
       LF_TRACE_END();
     }
-  } else if (kSplit && warp >= kMmaWarp0 && warp < kMmaWarp0 + 4) {
-    // ---------------- MMA issuers, bounded mode: two warps per query tile ----------
-    // In this mode the softmax is fast enough that instruction issue of the MMA side limits the
-    // loop (a thread sustains roughly one tcgen05.mma per 100 cycles next to the softmax warps),
-    // so each tile has one thread for O_t += P V (4 instructions per block) and one for
-    // S_t = Q_t K^T (8 per block). The scores of block j+2 overwrite the buffer that held
-    // P(j), so the QK thread waits for the completion of PV(j) (`pv_each`). All four threads
-    // walk every ring stage and each releases it (kv_empty counts four arrivals) once the MMAs
-    // it issued from the stage, if any, are complete.
-    if (lane == 0 && hi > lo) {
-      const int t = (warp - kMmaWarp0) & 1;
-      const bool is_qk = warp - kMmaWarp0 >= 2;
-      bool ok = true;
-      LF_TRACE_DECL(2, t == 0 && is_qk);
-      LF_TRACE_EV(0);
-      constexpr uint32_t kStageUnits = (2 * kKVTileBytes) >> 4;  // a stage is a pair of tiles
-      constexpr uint32_t kHalfUnits = kKVTileBytes >> 4;
-      const uint32_t s_col = tmem_base + t * 128;
-      const uint32_t o_col = tmem_base + kColO + t * 128;
-      auto active = [&](int j) { return has_work[t] && j >= lo_t[t] && j < hi_t[t]; };
-      int n = 0;  // ring position, walks the same sequence as the producer
-      auto wait_stage = [&](int where) -> int {  // next ring stage, waited full; -1 on time-out
-        const int stage = n % kStages;
-        const uint32_t parity = (n / kStages) & 1;
-        ++n;
-        if (!mbar_wait(&bars->kv_full[stage], parity)) {
-          report_timeout(p.status, where);
-          ok = false;
-          return -1;
-        }
-        return stage;
-      };
-      if (is_qk) {
-        if (has_work[t] && !mbar_wait(&bars->q_full[t], 0)) {
-          report_timeout(p.status, 2);
-          ok = false;
-        }
-        const uint64_t qdesc = make_smem_desc_sw128(smem_u32(sQ) + t * kQTileBytes, 16, 1024);
-        const uint64_t kdesc0 = make_smem_desc_sw128(smem_u32(sKV), 16, 1024);
-        auto issue_qk = [&](int stage, int hf, int j) {
-          const int buf = (j - lo_t[t]) & 1;
-          const uint64_t kd =
-              kdesc0 + static_cast<uint64_t>(stage * kStageUnits + hf * kHalfUnits);
-          const uint32_t d = s_col + buf * 64;
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            mma_ss(d, qdesc + static_cast<uint64_t>((ks / 4) * (kQBlockBytes >> 4) + (ks % 4) * 2),
-                   kd + static_cast<uint64_t>((ks / 4) * (kKVBlockBytes >> 4) + (ks % 4) * 2),
-                   kIdescQK, ks > 0 ? 1u : 0u);
-          }
-          tc_commit(&bars->s_full[t][buf]);
-        };
-        // Prologue: scores of the first two KV tiles (one stage).
-        if (ok) {
-          const int stage = wait_stage(3);
-          if (stage >= 0) {
-            tc_fence_after();
-            if (active(lo)) issue_qk(stage, 0, lo);
-            if (lo + 1 < hi && active(lo + 1)) issue_qk(stage, 1, lo + 1);
-            tc_commit(&bars->kv_empty[stage]);
-          }
-        }
-        for (int j = lo; j < hi && ok; ++j) {
-          LF_TRACE_EV(10);
-          const int st = wait_stage(4);  // {V(j), K(j+2)}
-          if (st < 0) break;
-          LF_TRACE_EV(11);
-          if (j + 2 < hi && active(j + 2)) {
-            if (active(j)) {
-              const int kt = j - lo_t[t];
-              if (!mbar_wait(&bars->pv_each[t][kt & 1], (kt >> 1) & 1)) {
-                report_timeout(p.status, 12 + t);
-                ok = false;
-                break;
-              }
-            }
-            tc_fence_after();
-            LF_TRACE_EV(13);
-            issue_qk(st, 1, j + 2);
-          }
-          tc_commit(&bars->kv_empty[st]);
-          LF_TRACE_EV(15);
-        }
-      } else {
-        const uint64_t vdesc0 = make_smem_desc_sw128(smem_u32(sKV), kKVBlockBytes, 1024);
-        {  // the first stage holds K tiles only
-          const int st = wait_stage(5);
-          if (st >= 0) tc_commit(&bars->kv_empty[st]);
-        }
-        for (int j = lo; j < hi && ok; ++j) {
-          const int st = wait_stage(5);  // {V(j), K(j+2)}
-          if (st < 0) break;
-          if (active(j)) {
-            const int kt = j - lo_t[t];
-            if (!mbar_wait(&bars->p_full[t][kt & 1], (kt >> 1) & 1)) {
-              report_timeout(p.status, 6 + t);
-              ok = false;
-              break;
-            }
-            tc_fence_after();
-            const uint64_t vd = vdesc0 + static_cast<uint64_t>(st * kStageUnits);
-            const uint32_t a = s_col + (kt & 1) * 64;
-#pragma unroll
-            for (int ks = 0; ks < kTileK / 16; ++ks) {
-              // P columns of 16 keys: 16 columns at the start of each 32-column half of S.
-              mma_ts(o_col, a + (ks >> 1) * 32 + (ks & 1) * 8,
-                     vd + static_cast<uint64_t>(ks * (2048 >> 4)), kIdescPV,
-                     (kt > 0 || ks > 0) ? 1u : 0u);
-            }
-            tc_commit(&bars->pv_each[t][kt & 1]);
-            if (j == hi_t[t] - 1) tc_commit(&bars->o_final[t]);
-          }
-          tc_commit(&bars->kv_empty[st]);
-        }
-      }
-      LF_TRACE_END();
-    }
-  } else if (!kSplit && (warp == kMmaWarp0 || warp == kMmaWarp0 + 1)) {
+  } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
     // ---------------- MMA issuers: one warp per query tile ----------
     // Two issuing threads halve the per-instruction issue overhead; the tensor pipe serialises
     // the two independent streams. Both walk the same K/V ring and both release every stage
@@ -502,226 +373,6 @@ __global__ void __launch_bounds__(prefill_threads(MODE), 1)
         LF_TRACE_EV(15);
       }
       LF_TRACE_END();
-    }
-  } else if constexpr (kSplit) {
-    // ---------------- softmax warps, bounded-score mode ----------------
-    // Four warpgroups: query tile t = warpgroup / 2; inside a tile, warpgroup `half` takes
-    // columns [32*half, 32*half + 32) of every 64-key block, one thread per (row, half). With
-    // the fixed reference there is no running max, no rescale of O and nothing to exchange
-    // between the two threads of a row until the final row sum.
-    const int wg = warp >> 2;
-    const int t = wg >> 1;
-    const int half = wg & 1;
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;  // row inside the tile == tensor-memory lane
-    const int grow = (iq0 + t) * kTileQ + row;
-    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t s_base = tmem_base + lane_addr + t * 128 + half * 32;
-    const uint32_t o_addr = tmem_base + lane_addr + kColO + t * 128;
-    float* l_slots = reinterpret_cast<float*>(sStage) + t * 256;  // [half][row]
-
-#ifndef LF_TRACE
-    if (p.dbg_ranges && tile_valid[t] && row == 0 && half == 0) {
-      const int64_t idx = ((static_cast<int64_t>(b) * p.Hq + h) * p.n_qtiles + (iq0 + t)) * 2;
-      p.dbg_ranges[idx] = lo_t[t];
-      p.dbg_ranges[idx + 1] = hi_t[t];
-    }
-#endif
-
-    if (has_work[t]) {
-      // Visible column interval of this row: [c_lo, c_hi].
-      int c_hi = p.Skv - 1;
-      int c_lo = 0;
-      if (p.mask_kind != LF_MASK_NONE) c_hi = min(c_hi, grow + p.causal_offset);
-      if (p.mask_kind == LF_MASK_CAUSAL_WINDOW)
-        c_lo = max(0, grow + p.causal_offset - (p.window - 1));
-
-      float l_run = 0.f;
-      bool ok = true;
-      const int nblk = hi_t[t] - lo_t[t];
-      // tanh(x) = x*(1 + y*(-1/3 + y*(2/15 + y*(-17/315)))), y = x^2, x = a*raw. The powers of a
-      // and the output factor c2 are folded into the coefficients p.qc[] on the host, so the
-      // polynomial runs on raw^2 and gives logit2 = raw * q(raw^2) directly; p.ylim[] are the
-      // limits of the two polynomials as bounds on raw^2.
-      const uint64_t q0c = pack2(p.qc[0], p.qc[0]);
-      const uint64_t q1c = pack2(p.qc[1], p.qc[1]);
-      // The tanh evaluation (0: degree 3, 1: degree 7, 2: MUFU) is chosen speculatively: a
-      // block starts with what the warp's previous block needed, and is redone on the spot
-      // with a stronger one if its own max |x| (known after the pass) asks for it.
-      int path = 0;
-      LF_TRACE_DECL(t, half == 0 && quarter == 0 && lane == 0);
-      for (int k = 0; k < nblk; ++k) {
-        const int c0 = (lo_t[t] + k) * kTileK + half * 32;  // first key column of this thread
-        const int buf = k & 1;
-        const uint32_t s_addr = s_base + buf * 64;
-        LF_TRACE_EV(20);
-        if (!mbar_wait(&bars->s_full[t][buf], (k >> 1) & 1)) {
-          report_timeout(p.status, 8 + t);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        LF_TRACE_EV(21);
-        const int rel_lo = c_lo - c0;  // visible columns of this thread's 32: [rel_lo, rel_hi]
-        const int rel_hi = c_hi - c0;
-        const bool masked = rel_lo > 0 || rel_hi < 31;
-
-        uint32_t pk[16];
-        float block_sum = 0.f;
-        for (;;) {
-          // (Read again from tensor memory when a block is redone: P is stored only at the end.)
-          uint32_t sr[32];
-          tmem_ld_32x32b_x32(s_addr, sr);
-          tmem_wait_ld();
-          LF_TRACE_EV(22);
-          float psum[4] = {0.f, 0.f, 0.f, 0.f};
-          float ymax0 = 0.f, ymax1 = 0.f;
-          auto finish_pair = [&](uint64_t z2, int i, bool apply_mask) {
-            float z0, z1;
-            unpack2(z2, z0, z1);
-            if (apply_mask) {
-              if (i < rel_lo || i > rel_hi) z0 = -INFINITY;
-              if (i + 1 < rel_lo || i + 1 > rel_hi) z1 = -INFINITY;
-            }
-            // Every exponential goes to MUFU here: this loop is bound by instruction dispatch,
-            // and two ex2 cost less of it than their FMA-pipe emulation.
-            const uint32_t pkv = pack_bf16x2(ex2_approx(z0), ex2_approx(z1));
-            pk[i >> 1] = pkv;
-            // The row sum is taken over the bf16-rounded values that the PV product sees, so that
-            // numerator and denominator carry the same rounding (it matters here because the
-            // largest P of a row is not exactly 1 as it is with a running max). The mixed
-            // precision add reads the bf16 halves directly.
-            if ((i >> 1) & 1) add_bf16x2_to_f32(psum[2], psum[3], pkv);
-            else add_bf16x2_to_f32(psum[0], psum[1], pkv);
-          };
-          auto body = [&](auto path_tag, bool apply_mask) {
-            constexpr int kPath = decltype(path_tag)::value;
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const uint64_t r2 = pack2u(sr[i], sr[i + 1]);
-              const uint64_t y2 = mul2(r2, r2);
-              float y0, y1;
-              unpack2(y2, y0, y1);
-              if ((i >> 1) & 1) ymax1 = max3(ymax1, y0, y1); else ymax0 = max3(ymax0, y0, y1);
-              uint64_t z2;
-              if constexpr (kPath == 0) {
-                z2 = mul2(r2, fma2(y2, q1c, q0c));
-              } else if constexpr (kPath == 1) {
-                uint64_t q2 = fma2(y2, pack2(p.qc[3], p.qc[3]), pack2(p.qc[2], p.qc[2]));
-                q2 = fma2(q2, y2, q1c);
-                q2 = fma2(q2, y2, q0c);
-                z2 = mul2(r2, q2);
-              } else {
-                const float t0 = tanh_approx(__uint_as_float(sr[i]) * p.a);
-                const float t1 = tanh_approx(__uint_as_float(sr[i + 1]) * p.a);
-                z2 = mul2(pack2(t0, t1), pack2(p.c2, p.c2));
-              }
-              finish_pair(z2, i, apply_mask);
-            }
-          };
-          if (path == 0) {
-            if (masked) body(std::integral_constant<int, 0>{}, true);
-            else body(std::integral_constant<int, 0>{}, false);
-          } else if (path == 1) {
-            if (masked) body(std::integral_constant<int, 1>{}, true);
-            else body(std::integral_constant<int, 1>{}, false);
-          } else {
-            if (masked) body(std::integral_constant<int, 2>{}, true);
-            else body(std::integral_constant<int, 2>{}, false);
-          }
-          block_sum = (psum[0] + psum[1]) + (psum[2] + psum[3]);
-          // What this block needed, over the whole warp (masked columns included: their raw
-          // scores are ordinary finite numbers).
-          const float ymax = fmaxf(ymax0, ymax1);
-          const unsigned mine = ymax > p.ylim[1] ? 2u : (ymax > p.ylim[0] ? 1u : 0u);
-          const int needed = static_cast<int>(__reduce_max_sync(0xffffffffu, mine));
-          const bool redo = needed > path;
-          path = needed;
-          if (!redo) break;
-        }
-        l_run += block_sum;
-        LF_TRACE_EV(24);
-        // P (bf16, two per column) goes on top of the first 16 of this thread's S columns.
-        tmem_st_32x32b_x16(s_addr, pk);
-        tmem_wait_st();
-        tc_fence_before();
-        // One arrival per warp (256 arrivals on one barrier word would serialise).
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->p_full[t][buf]);
-        LF_TRACE_EV(25);
-      }
-      LF_TRACE_EV(26);
-
-      // Row sum: the two halves meet in shared memory.
-      if (ok) {
-        l_slots[half * 128 + row] = l_run;
-        mbar_arrive(&bars->l_ready[t]);
-        if (!mbar_wait(&bars->l_ready[t], 0)) {
-          report_timeout(p.status, 18 + t);
-          ok = false;
-        }
-        l_run = l_slots[row] + l_slots[128 + row];
-      }
-      // Epilogue: O_t / l -> bf16 -> global; each half writes D/2 of the row's columns.
-      if (ok) {
-        if (!mbar_wait(&bars->o_final[t], 0)) {
-          report_timeout(p.status, 10 + t);
-          ok = false;
-        }
-      }
-      if (ok) {
-        tc_fence_after();
-        const float inv = 1.f / l_run;
-        // Each warp owns 32 rows. A 32-column chunk (64 bytes per row) goes through a swizzled
-        // 2 KB buffer of the warp so that one store instruction writes eight 64-byte row
-        // segments instead of thirty-two 16-byte pieces. The buffers sit in the tile's own Q
-        // area, which nothing reads once the last MMA of the tile has completed.
-        unsigned char* stage = sQ + t * kQTileBytes + (warp & 7) * 2048;
-        __nv_bfloat16* obase = p.out + b * p.o_stride[0] + h * p.o_stride[1];
-        const int row0 = (iq0 + t) * kTileQ + quarter * 32;  // first global row of the warp
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c) {
-          const int col = half * (D / 2) + c * 32;
-          uint32_t orr[32];
-          tmem_ld_32x32b_x32(o_addr + col, orr);
-          tmem_wait_ld();
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {  // piece q of row r sits at position q ^ ((r >> 1) & 3)
-            uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(orr[8 * q]) * inv,
-                              __uint_as_float(orr[8 * q + 1]) * inv);
-            w.y = pack_bf16x2(__uint_as_float(orr[8 * q + 2]) * inv,
-                              __uint_as_float(orr[8 * q + 3]) * inv);
-            w.z = pack_bf16x2(__uint_as_float(orr[8 * q + 4]) * inv,
-                              __uint_as_float(orr[8 * q + 5]) * inv);
-            w.w = pack_bf16x2(__uint_as_float(orr[8 * q + 6]) * inv,
-                              __uint_as_float(orr[8 * q + 7]) * inv);
-            *reinterpret_cast<uint4*>(stage + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) = w;
-          }
-          __syncwarp();
-#pragma unroll
-          for (int rr = 0; rr < 4; ++rr) {
-            const int r = rr * 8 + (lane >> 2);
-            const int q = lane & 3;
-            const uint4 w =
-                *reinterpret_cast<const uint4*>(stage + r * 64 + ((q ^ ((r >> 1) & 3)) << 4));
-            if (row0 + r < p.Sq)
-              *reinterpret_cast<uint4*>(obase + static_cast<int64_t>(row0 + r) * p.o_stride[2] +
-                                        col + q * 8) = w;
-          }
-          __syncwarp();
-        }
-      }
-      LF_TRACE_EV(27);
-      LF_TRACE_END();
-    } else if (tile_valid[t] && grow < p.Sq && half == 0) {
-      // No visible key at all for this tile: softmax of an all -inf row is NaN in the
-      // eager computation, so the rows are written as NaN.
-      __nv_bfloat16* orow = p.out + b * p.o_stride[0] + h * p.o_stride[1] +
-                            static_cast<int64_t>(grow) * p.o_stride[2];
-      const uint4 nan4 = {0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u};
-#pragma unroll
-      for (int c = 0; c < D; c += 8) *reinterpret_cast<uint4*>(orow + c) = nan4;
     }
   } else {
     // ---------------- softmax warps ----------------
@@ -1137,7 +788,7 @@ static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CU
   }
   const int pairs = (p.n_qtiles + 1) / 2;
   dim3 grid(pairs, p.Hq, B);
-  prefill_kernel<D, MODE><<<grid, prefill_threads(MODE), smem, st>>>(mq, mk, mv, p);
+  prefill_kernel<D, MODE><<<grid, kPrefillThreads, smem, st>>>(mq, mk, mv, p);
   return check_launch("prefill_kernel");
 }
 
@@ -1297,18 +948,12 @@ static int prefill_impl(const LfPrefillArgs* a, void* stream) {
   if (a->D == 128) {
     if (mode == kModeNone) return launch_prefill<128, kModeNone>(mq, mk, mv, p, a->B, st);
     if (mode == kModeSoftcap) return launch_prefill<128, kModeSoftcap>(mq, mk, mv, p, a->B, st);
-#ifndef LF_NO_PERSISTENT
     if (mode == kModeBounded) return launch_prefill_bounded<128>(mq, mk, mv, mo, p, a->B, st);
-#endif
-    if (mode == kModeBounded) return launch_prefill<128, kModeBounded>(mq, mk, mv, p, a->B, st);
     return launch_prefill<128, kModeGeneric>(mq, mk, mv, p, a->B, st);
   }
   if (mode == kModeNone) return launch_prefill<64, kModeNone>(mq, mk, mv, p, a->B, st);
   if (mode == kModeSoftcap) return launch_prefill<64, kModeSoftcap>(mq, mk, mv, p, a->B, st);
-#ifndef LF_NO_PERSISTENT
   if (mode == kModeBounded) return launch_prefill_bounded<64>(mq, mk, mv, mo, p, a->B, st);
-#endif
-  if (mode == kModeBounded) return launch_prefill<64, kModeBounded>(mq, mk, mv, p, a->B, st);
   return launch_prefill<64, kModeGeneric>(mq, mk, mv, p, a->B, st);
 }
 

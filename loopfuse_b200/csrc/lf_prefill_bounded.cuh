@@ -1,10 +1,24 @@
-// Persistent form of the bounded-score prefill kernel (included by lf_prefill.cu).
+// Prefill attention for softcap scores of bounded range, persistent form (included by
+// lf_prefill.cu, which holds the shared definitions and the host side).
 //
-// Same tiles, roles and tensor-memory layout as prefill_kernel<D, kModeBounded>, but one CTA per
-// SM walks a queue of work items (one item = two consecutive query tiles of one (batch, head)),
-// taken from a ticket counter in the launch order of the non-persistent grid (the query-tile pairs
-// of one head next to each other, heaviest first, so that they run at the same time on different
-// SMs and share K/V through L2). Nothing drains between items:
+// Softcap gives logit2 = c2 * tanh(a * raw) with |logit2| <= c2; when c2 <= 80, exp2(logit2) can
+// be taken against the fixed reference 0 instead of a running row max. Then the blocks of a row
+// are independent, O is never rescaled, and a row can be split between two threads with nothing
+// to exchange but the final row sum. 672 threads:
+//   warps 0-7   softmax for query tile 0: two threads per score row, 32 columns of a block each
+//   warps 8-15  softmax for query tile 1
+//   warp  16    TMA producer and item dispatcher
+//   warps 17/18 PV issuers of tile 0 / 1, warps 19/20 QK^T issuers of tile 0 / 1 (one thread
+//               each; instruction issue limits the MMA side, so the two products have their own
+//               threads; the scores of block j+2 reuse the buffer that held P(j), so the QK^T
+//               thread waits for the completion of PV(j))
+// Tensor memory as in prefill_kernel, except that P (bf16) overwrites the first 16 columns of
+// each 32-column half of its S buffer (each thread stores over its own scores).
+//
+// One CTA per SM walks a queue of work items (one item = two consecutive query tiles of one
+// (batch, head)), taken from a ticket counter in the launch order of the non-persistent grid
+// (the query-tile pairs of one head next to each other, heaviest first, so that they run at the
+// same time on different SMs and share K/V through L2). Nothing drains between items:
 //   - the K/V ring just continues with the next item's tiles;
 //   - the S buffers of a tile keep alternating (buffer = running block count of the tile & 1), so
 //     the first scores of the next item are computed while the last blocks of this one are still
@@ -12,7 +26,9 @@
 //   - Q_t of the next item is fetched as soon as the last QK^T of this item has read Q_t
 //     (`q_free`), which is two blocks before the item ends;
 //   - the only wait the hand-over adds is O_t: the first PV of the next item starts when the
-//     epilogue has read O_t out of tensor memory (`o_free`).
+//     epilogue has read O_t out of tensor memory (`o_free`);
+//   - the output leaves through TMA bulk stores from a small staging buffer per warp, so the
+//     load/store unit of the SM is not tied up by 128 scattered row segments per warp.
 #pragma once
 
 namespace lf {
