@@ -553,6 +553,10 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
             unpack2(r2, r0, r1);
             p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23));
             p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
+            if (apply_mask) {  // the clamp above would leave 2^-120 in a masked position
+              if (z0 == -INFINITY) p0 = 0.f;
+              if (z1 == -INFINITY) p1 = 0.f;
+            }
           } else {
             p0 = ex2_approx(z0);
             p1 = ex2_approx(z1);

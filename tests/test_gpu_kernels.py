@@ -295,6 +295,74 @@ def test_kernel_iterates_exactly_the_analysed_skip_ranges(kind, W, S_):
                                                      keep=keep)
 
 
+@pytest.mark.parametrize("kind,W,S_", [(S.MASK_CAUSAL, 0, 2048), (S.MASK_CAUSAL_WINDOW, 256, 2048),
+                                       (S.MASK_CAUSAL_WINDOW, 130, 593), (S.MASK_NONE, 0, 400)])
+def test_persistent_softcap_kernel_iterates_exactly_the_analysed_skip_ranges(kind, W, S_):
+    """The same bit-exact check for the persistent kernel that softcap(50) selects (more work
+    items than SMs, so every CTA walks several items)."""
+    B, H, D = 3, 32, 64
+    q, k, v = _prefill_case(B, H, 8, S_, S_, D)
+    n_qt = -(-S_ // S.TILE_Q)
+    dbg = torch.full((B * H * n_qt * 2,), -1, dtype=torch.int32, device=DEV)
+    _run_prefill(q, k, v, scale=0.125, mods=SOFTCAP, mask_kind=kind, window=W, dbg_ranges=dbg)
+    got = dbg.view(B * H, n_qt, 2).cpu()
+    table = S.skip_table(kind, W, 0, S_, S_)
+    for iq in range(n_qt):
+        assert all(tuple(got[u, iq].tolist()) == table[iq] for u in range(B * H))
+
+
+@pytest.mark.parametrize("S_,W", [(593, 0), (1024, 200), (130, 64)])
+def test_prefill_softcap_head_dim_64(S_, W):
+    q, k, v = _prefill_case(2, 4, 2, S_, S_, 64, scale=1.5)
+    kind = S.MASK_CAUSAL_WINDOW if W else S.MASK_CAUSAL
+    out = _run_prefill(q, k, v, scale=64 ** -0.5, mods=SOFTCAP, mask_kind=kind, window=W)
+    want = O.attention_ref(q, k, v, mods=O.softcap_mods(50.0), mask="window" if W else "causal",
+                           window=W, batch_chunk=2)
+    assert max_err(out, want) <= TOL
+
+
+def test_prefill_softcap_large_cap_uses_running_max():
+    """cap * log2(e) > 80: outside the fixed-reference range, the running-max kernel runs."""
+    cap = 100.0
+    mods = [ScoreMod(S.MOD_DIV, cap), ScoreMod(S.MOD_TANH), ScoreMod(S.MOD_MUL, cap)]
+    q, k, v = _prefill_case(1, 4, 2, 593, 593, 128, scale=2.0)
+    out = _run_prefill(q, k, v, scale=128 ** -0.5, mods=mods, mask_kind=S.MASK_CAUSAL)
+    want = O.attention_ref(q, k, v, mods=O.softcap_mods(cap), mask="causal")
+    assert max_err(out, want) <= TOL
+
+
+@pytest.mark.parametrize("softcap", [False, True])
+def test_prefill_rows_without_visible_keys_are_nan(softcap):
+    """Diagonal shifted up by 200: query rows 0..199 see no key at all (NaN in the eager
+    computation), row 200 sees key 0 only; the first 128-row tile has no KV block to visit."""
+    q, k, v = _prefill_case(1, 2, 2, 384, 256, 128)
+    mods = SOFTCAP if softcap else []
+    out = _run_prefill(q, k, v, scale=128 ** -0.5, mods=mods, mask_kind=S.MASK_CAUSAL,
+                       causal_offset=-200).float().cpu()
+    want = O.attention_ref(q, k, v, mods=O.softcap_mods(50.0) if softcap else (),
+                           mask="causal", offset=-200)
+    assert torch.isnan(want[:, :, :200]).all() and not torch.isnan(want[:, :, 200:]).any()
+    assert torch.isnan(out[:, :, :200]).all()
+    assert (out[:, :, 200:] - want[:, :, 200:]).abs().max().item() <= TOL
+    assert torch.equal(out[:, :, 200], v[:, :, 0].float())
+
+
+def test_persistent_kernel_launches_on_two_streams():
+    """Launches that overlap on the GPU use different ticket counters."""
+    q, k, v = (t.to(DEV) for t in _prefill_case(2, 8, 8, 1024, 1024, 128))
+    kw = dict(scale=128 ** -0.5, mods=SOFTCAP, mask_kind=S.MASK_CAUSAL)
+    ref = F.prefill_attention(q, k, v, **kw)
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream() for _ in range(2)]
+    outs = []
+    for i in range(6):
+        with torch.cuda.stream(streams[i % 2]):
+            outs.append(F.prefill_attention(q, k, v, **kw))
+    torch.cuda.synchronize()
+    for o in outs:
+        assert torch.equal(o, ref)
+
+
 def test_prefill_config2_full_size_sample():
     """cfg 2 at full size on the GPU; the oracle checks batch elements 0 and 7 (it needs ~10 s
     per element on the CPU)."""
