@@ -319,7 +319,7 @@ __global__ void __launch_bounds__(kDecodeThreads)
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void mma_16816_rows0to7(float& d0, float& d1, uint32_t a0, uint32_t a2,
                                                    uint32_t b0, uint32_t b1) {
-  float unused2, unused3;  // rows 8..15 of the tile are padding
+  [[maybe_unused]] float unused2, unused3;  // rows 8..15 of the tile are padding
   asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
       "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %10, %11};"
       : "+f"(d0), "+f"(d1), "=f"(unused2), "=f"(unused3)

@@ -486,11 +486,19 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
         LF_TRACE_EV(21);
         const int rel_lo = c_lo - c0;  // visible columns of this thread's 32: [rel_lo, rel_hi]
         const int rel_hi = c_hi - c0;
-        const bool masked = rel_lo > 0 || rel_hi < 31;
+        // Warp-uniform decisions (the 32 x 32 piece of the block that this warp owns is fully
+        // visible, crossed by a mask edge, or fully hidden), so that a warp never runs both
+        // forms of the pass and a hidden piece costs nothing.
+        const bool masked = __any_sync(0xffffffffu, rel_lo > 0 || rel_hi < 31);
+        const bool hidden = __all_sync(0xffffffffu, rel_lo > 31 || rel_hi < 0);
 
         uint32_t pk[16];
         float block_sum = 0.f;
-        for (;;) {
+        if (hidden) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pk[i] = 0u;
+        }
+        while (!hidden) {
           // (Read again from tensor memory when a block is redone: P is stored only at the end.)
           uint32_t sr[32];
           tmem_ld_32x32b_x32(s_addr, sr);
