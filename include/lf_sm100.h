@@ -141,7 +141,16 @@ const char* lf_strerror(int status);
 /* Text of the last CUDA error seen by this thread inside the library ("" if none). */
 const char* lf_last_cuda_error(void);
 
-/* Prefill attention: out = softmax(mask(mod(scale * q k^T))) v, online softmax, tcgen05 MMA. */
+/* Prefill attention: out = softmax(mask(mod(scale * q k^T))) v, online softmax, tcgen05 MMA.
+ * A score-mod chain of the softcap form (MUL|DIV)* TANH (MUL|DIV)* with cap * log2(e) <= 80 (and
+ * Skv <= 2^22) runs a persistent kernel that takes exp2 against the fixed reference 0 instead
+ * of a running row max: P lies in [2^-80, 2^80], row sums and outputs are accumulated in fp32.
+ * That is exact softmax arithmetic (same result within the bf16 tolerance) as long as
+ * Skv * max|v| stays below about 2^46 (e.g. |v| < 2^24 at the largest Skv); beyond that the fp32
+ * accumulators can overflow where the running-max form would not. Every other chain uses the
+ * running-max kernel. The persistent kernel keeps its work-queue counters in the library image
+ * (256 slots taken round-robin and zeroed in stream order): more than 256 such launches in
+ * flight at once on one device could share a counter. */
 int lf_prefill_bf16(const LfPrefillArgs* args, void* stream);
 
 /* KV-tile range [lo, hi) that q-tile `iq` must visit; the same integers the kernel uses. */
