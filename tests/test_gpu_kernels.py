@@ -387,3 +387,31 @@ def test_prefill_config3_full_size_sample():
     assert max_err(out[3:4], want) <= TOL
     kv_rep = v[:, :, 0, :].repeat_interleave(w.group, dim=1)
     assert torch.equal(out[:, :, 0, :].cpu(), kv_rep)
+
+
+def test_prefill_and_decode_replay_from_a_cuda_graph():
+    """The entry points only enqueue work on the given stream (a memset node for the work-queue
+    counter, kernel nodes with the tensor maps passed by value), so after one eager call they can
+    be captured once and replayed on new data in the same buffers."""
+    q, k, v = (t.to(DEV) for t in _prefill_case(1, 4, 2, 640, 640, 128))
+    kw = dict(scale=128 ** -0.5, mods=SOFTCAP, mask_kind=S.MASK_CAUSAL)
+    qd = randn_bf16(2, 2, 4, 128, seed=21).to(DEV)
+    kd, vd = (randn_bf16(2, 2, 777, 128, seed=s_).to(DEV) for s_ in (22, 23))
+    ws = F.DecodeWorkspace()
+    out_p = torch.empty_like(q)
+    F.prefill_attention(q, k, v, out=out_p, **kw)             # first calls outside the capture
+    out_d = F.decode_attention(qd, kd, vd, scale=0.09, workspace=ws)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        F.prefill_attention(q, k, v, out=out_p, **kw)
+        out_d2 = F.decode_attention(qd, kd, vd, scale=0.09, workspace=ws, out=out_d)
+    for seed in (31, 32):
+        q.copy_(randn_bf16(*q.shape, seed=seed))
+        qd.copy_(randn_bf16(*qd.shape, seed=seed + 10))
+        g.replay()
+        torch.cuda.synchronize()
+        want_p = O.attention_ref(q, k, v, mods=O.softcap_mods(50.0), mask="causal")
+        assert max_err(out_p, want_p) <= TOL
+        want_d = O.attention_ref(qd.reshape(2, 8, 1, 128), kd, vd, scale=0.09).reshape(2, 2, 4, 128)
+        assert max_err(out_d2, want_d) <= TOL
