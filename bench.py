@@ -40,8 +40,8 @@ METRIC = "prefill TFLOP/s (causal-adjusted FLOPs) per job; decode HBM GB/s under
 # workload's dominant kernel, from the ncu captures summarised under profiles/: captured on a
 # smaller batch and scaled by the batch ratio (the traffic is proportional to the batch).
 NCU_TRAFFIC_BYTES = {
-    "causal_softcap": 4 * (100.74e6 + 15.14e6),
-    "window_gqa_softcap": 2 * (100.75e6 + 36.66e6),
+    "causal_softcap": 4 * (100.74e6 + 15.15e6),
+    "window_gqa_softcap": 2 * (100.74e6 + 36.01e6),
     "decode": 8 * (268.51e6 + 4.59e6),
     "paged_decode_gqa": 2 * (268.79e6 + 4.74e6),
 }
