@@ -271,15 +271,22 @@ def run_ours(args, workload) -> None:
         gathered = torch.empty((world * w.B, *runners[0][2].shape[1:]), dtype=torch.bfloat16,
                                device=dev)
 
+    align_token = torch.zeros(1, device=dev)
     for i in range(max(args.warmup, 3)):
         runners[i % 2][0]()
     if world > 1:
+        dist.all_reduce(align_token)
         gather_output(runners[0][2], tuple(gathered.shape), out=gathered)
     barrier()
     sampler = ClockSampler(physical_gpu_index(local_rank))
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev_compute_end = torch.cuda.Event(enable_timing=True)
     with sampler:
+        if world > 1:
+            # The host-side barrier above lets the ranks' CPUs leave milliseconds apart; a tiny
+            # all-reduce enqueued ahead of the start event lines the GPU timelines up instead, so
+            # that the one collective at the end does not wait for a rank whose host was late.
+            dist.all_reduce(align_token)
         start.record()
         for i in range(args.steps):
             runners[i % 2][0]()
