@@ -415,3 +415,18 @@ def test_prefill_and_decode_replay_from_a_cuda_graph():
         assert max_err(out_p, want_p) <= TOL
         want_d = O.attention_ref(qd.reshape(2, 8, 1, 128), kd, vd, scale=0.09).reshape(2, 2, 4, 128)
         assert max_err(out_d2, want_d) <= TOL
+
+
+def test_persistent_kernel_ticket_counters_wrap_around():
+    """More launches than the library has work-queue counters (256): slots are reused in stream
+    order and every launch still walks the whole queue."""
+    q, k, v = (t.to(DEV) for t in _prefill_case(1, 8, 4, 512, 512, 64))
+    kw = dict(scale=0.125, mods=SOFTCAP, mask_kind=S.MASK_CAUSAL)
+    ref = F.prefill_attention(q, k, v, **kw).clone()
+    out = torch.empty_like(ref)
+    for i in range(600):
+        if i % 100 == 99:
+            out.zero_()
+        F.prefill_attention(q, k, v, out=out, **kw)
+        if i % 100 == 99:
+            assert torch.equal(out, ref)
