@@ -216,8 +216,8 @@ def make_runner(workload, inputs):
         def fn():
             F.paged_decode_attention(q, kp, vp, table, scale=scale, out=out, workspace=ws)
     from loopfuse_b200 import _native
-    splits = _native.load().lf_decode_auto_splits(w.B, w.Hkv, w.group, w.S, w.D,
-                                                  int(w.kind == "paged_decode"))
+    splits = _native.load().lf_decode_auto_splits(
+        w.B, w.Hkv, w.group, w.S, w.D, w.page_size if w.kind == "paged_decode" else 0)
     return fn, (2 if splits > 1 else 1), out
 
 

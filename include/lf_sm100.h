@@ -25,6 +25,11 @@
  *                          indexing bit for bit.
  *   lf_skip_range          the loop-range rewrite of the sparsity pass,
  *                          loopfuse/compiler/passes/skip_loop_iterations.py:343-376.
+ *   lf_kv_append_bf16      the write side of the paged cache the two-level load reads: the
+ *                          cache / block-table layout of tests/benchmark.py:308-319 and the
+ *                          index rule of loopfuse/torch_backend/__init__.py:46-63
+ *                          (out = buffer[block_table]), used as a store address. The reference
+ *                          fills its caches on the host with torch.randn.
  */
 #ifndef LF_SM100_H_
 #define LF_SM100_H_
@@ -36,7 +41,7 @@
 extern "C" {
 #endif
 
-#define LF_ABI_VERSION 1
+#define LF_ABI_VERSION 2
 
 typedef enum {
   LF_OK = 0,
@@ -72,9 +77,12 @@ typedef enum {
 #define LF_MOD_DIV 10    /* s /= arg   */
 #define LF_MAX_MODS 8
 
-/* Prefill tile shape the sm_100a kernel uses; skip ranges are defined on it. */
+/* Prefill tile shapes of the sm_100a kernels; skip ranges are defined on them. Query tiles are
+ * always 128 rows; KV tiles are 64 keys, or 128 keys in the wide bounded-softcap kernel (see
+ * lf_prefill_kv_tile). */
 #define LF_PREFILL_TILE_Q 128
 #define LF_PREFILL_TILE_K 64
+#define LF_PREFILL_TILE_K_WIDE 128
 
 typedef struct {
   const void* q;      /* bf16 [B, Hq,  Sq,  D], innermost stride 1 */
@@ -95,7 +103,10 @@ typedef struct {
   int32_t causal_offset;/* 0 for square scores */
   int32_t* status;      /* optional device word */
   int32_t* dbg_ranges;  /* optional device int32 [B*Hq*ceil(Sq/128)*2]: the (lo,hi) range of
-                           64-key KV tiles each q-tile actually iterated (bit-exact check) */
+                           KV tiles (of lf_prefill_kv_tile(args) keys) each q-tile actually
+                           iterated (bit-exact check against lf_skip_range) */
+  int32_t kv_tile;      /* 0 = the library picks; 64 or 128 pins the KV tile of the kernel
+                           (128 exists only for the bounded-softcap kernel) */
 } LfPrefillArgs;
 
 typedef struct {
@@ -126,6 +137,28 @@ typedef struct {
 } LfDecodeArgs;
 
 typedef struct {
+  const void* k_new;    /* bf16 [B, Hkv, T, D]: T new key rows per sequence, innermost stride 1 */
+  const void* v_new;    /* bf16 [B, Hkv, T, D] */
+  void* k_pool;         /* bf16 [n_pages, page_size, Hkv, D] (page_size 1: [n_pages, Hkv, D]) */
+  void* v_pool;
+  const int32_t* block_table;   /* int32 [B, bt_blocks]: pages of K (and of V) */
+  const int32_t* block_table_v; /* pages of V when they differ from K's; NULL = same table */
+  const int32_t* seq_pos;       /* device int32 [B]: logical position of each sequence's first
+                                   new token; NULL = start_pos for every sequence */
+  int32_t start_pos;
+  int32_t B, Hkv, T, D;         /* D in {64, 128} */
+  int64_t kn_stride[3];         /* element strides of k_new dims (b, hkv, t) */
+  int64_t vn_stride[3];
+  int64_t kp_stride[3];         /* element strides of k_pool dims (page, slot, hkv) */
+  int64_t vp_stride[3];
+  int64_t bt_stride;            /* elements between rows of block_table */
+  int32_t bt_blocks;            /* entries per row of block_table */
+  int32_t page_size;
+  int32_t n_pages;
+  int32_t* status;              /* optional device word */
+} LfKvAppendArgs;
+
+typedef struct {
   int32_t abi_version;
   int32_t device;         /* current CUDA device ordinal */
   int32_t cc_major, cc_minor;
@@ -152,6 +185,14 @@ const char* lf_last_cuda_error(void);
  * (256 slots taken round-robin and zeroed in stream order): more than 256 such launches in
  * flight at once on one device could share a counter. */
 int lf_prefill_bf16(const LfPrefillArgs* args, void* stream);
+/* KV tile size (64 or 128 keys) of the kernel lf_prefill_bf16 would run for these arguments, or
+ * a negative LfStatus; launches nothing. Skip ranges and `dbg_ranges` are in units of it.
+ * Replaces the tile sizes the reference autotunes per kernel (loopfuse/codegen.py:360-393). */
+int lf_prefill_kv_tile(const LfPrefillArgs* args);
+/* Hit / miss counters of the library's cache of encoded tensor maps (keyed by address, shape,
+ * strides and box; the per-call host work the reference's launcher repeats on every call,
+ * loopfuse/codegen.py:215-298). Either pointer may be NULL. */
+void lf_tile_map_cache_stats(uint64_t* hits, uint64_t* misses);
 
 /* KV-tile range [lo, hi) that q-tile `iq` must visit; the same integers the kernel uses. */
 void lf_skip_range(int32_t mask_kind, int32_t window, int32_t causal_offset, int32_t Sq,
@@ -161,9 +202,13 @@ void lf_skip_range(int32_t mask_kind, int32_t window, int32_t causal_offset, int
 /* Decode attention (Sq == 1 per head, G grouped heads per kv head), split over KV. */
 int lf_decode_bf16(const LfDecodeArgs* args, void* stream);
 int lf_decode_paged_bf16(const LfDecodeArgs* args, void* stream);
-/* Split count the library picks for splits == 0, and the workspace it then needs. */
+/* Split count the library picks for splits == 0, and the workspace it then needs. `page_size`
+ * is 0 for a dense cache, else the tokens per page of the paged cache (a split's slice of the
+ * block table is staged in shared memory; with small pages and a long context the library splits
+ * further until the slice fits, and an explicit split count that leaves it too large is refused
+ * with LF_ERR_TOO_LARGE). */
 int lf_decode_auto_splits(int32_t B, int32_t Hkv, int32_t G, int32_t Skv, int32_t D,
-                          int32_t paged);
+                          int32_t page_size);
 size_t lf_decode_workspace_bytes(int32_t B, int32_t Hkv, int32_t G, int32_t D, int32_t splits);
 
 /* Decode for callers that cannot allocate. No counterpart in the reference (it has neither
@@ -196,6 +241,15 @@ int lf_paged_gather_bf16(const void* pool, const int32_t* block_table, void* out
                          int32_t Hkv, int32_t Skv, int32_t D, int32_t page_size, int32_t n_pages,
                          const int64_t* pool_stride, int64_t bt_stride, int32_t* status,
                          void* stream);
+
+/* Append to a paged KV cache: new token i of sequence b (logical position pos = seq_pos[b] + i,
+ * or start_pos + i) is written to
+ *     pool[block_table[b, pos / page_size], pos % page_size, kv head, :]
+ * for K and for V - the address rule lf_decode_paged_bf16 and lf_paged_gather_bf16 read with.
+ * Pure data movement (bit-exact). A position the table has no entry for, or a page id outside
+ * [0, n_pages), is reported as LF_DEV_BAD_PAGE in `status` and that row is not written (the
+ * kernel never stores outside the pools). Rows of different sequences must not share a page. */
+int lf_kv_append_bf16(const LfKvAppendArgs* args, void* stream);
 
 #ifdef __cplusplus
 }

@@ -16,7 +16,8 @@ EXPORTS = [
     "lf_query", "lf_strerror", "lf_last_cuda_error", "lf_prefill_bf16", "lf_skip_range",
     "lf_decode_bf16", "lf_decode_paged_bf16", "lf_decode_auto_splits",
     "lf_decode_workspace_bytes", "lf_combine_f32", "lf_paged_gather_bf16",
-    "lf_decode_bf16_static",
+    "lf_decode_bf16_static", "lf_prefill_kv_tile", "lf_tile_map_cache_stats",
+    "lf_kv_append_bf16",
 ]
 
 LF_STATIC_SCRATCH_BYTES = 8 << 20
@@ -32,7 +33,7 @@ class LfPrefillArgs(C.Structure):
         ("scale", C.c_float), ("n_mod", C.c_int32),
         ("mod_op", C.c_int32 * LF_MAX_MODS), ("mod_arg", C.c_float * LF_MAX_MODS),
         ("mask_kind", C.c_int32), ("window", C.c_int32), ("causal_offset", C.c_int32),
-        ("status", C.c_void_p), ("dbg_ranges", C.c_void_p),
+        ("status", C.c_void_p), ("dbg_ranges", C.c_void_p), ("kv_tile", C.c_int32),
     ]
 
 
@@ -49,6 +50,19 @@ class LfDecodeArgs(C.Structure):
         ("page_size", C.c_int32), ("n_pages", C.c_int32),
         ("splits", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("status", C.c_void_p),
+    ]
+
+
+class LfKvAppendArgs(C.Structure):
+    _fields_ = [
+        ("k_new", C.c_void_p), ("v_new", C.c_void_p), ("k_pool", C.c_void_p),
+        ("v_pool", C.c_void_p), ("block_table", C.c_void_p), ("block_table_v", C.c_void_p),
+        ("seq_pos", C.c_void_p), ("start_pos", C.c_int32),
+        ("B", C.c_int32), ("Hkv", C.c_int32), ("T", C.c_int32), ("D", C.c_int32),
+        ("kn_stride", C.c_int64 * 3), ("vn_stride", C.c_int64 * 3),
+        ("kp_stride", C.c_int64 * 3), ("vp_stride", C.c_int64 * 3),
+        ("bt_stride", C.c_int64), ("bt_blocks", C.c_int32), ("page_size", C.c_int32),
+        ("n_pages", C.c_int32), ("status", C.c_void_p),
     ]
 
 
@@ -81,6 +95,12 @@ def load() -> C.CDLL:
     lib.lf_last_cuda_error.restype = C.c_char_p
     lib.lf_prefill_bf16.argtypes = [C.POINTER(LfPrefillArgs), C.c_void_p]
     lib.lf_prefill_bf16.restype = C.c_int
+    lib.lf_prefill_kv_tile.argtypes = [C.POINTER(LfPrefillArgs)]
+    lib.lf_prefill_kv_tile.restype = C.c_int
+    lib.lf_tile_map_cache_stats.argtypes = [C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
+    lib.lf_tile_map_cache_stats.restype = None
+    lib.lf_kv_append_bf16.argtypes = [C.POINTER(LfKvAppendArgs), C.c_void_p]
+    lib.lf_kv_append_bf16.restype = C.c_int
     lib.lf_skip_range.argtypes = [C.c_int32] * 8 + [C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     lib.lf_skip_range.restype = None
     for name in ("lf_decode_bf16", "lf_decode_paged_bf16", "lf_decode_bf16_static"):

@@ -11,6 +11,11 @@ Environment flags (reference: interface.py:23-29):
   ``CODEGEN_ONLY=1``  analysis only - the compiled callable returns the ``AttentionPlan`` instead
                       of launching (works on hosts without a GPU);
   ``DEBUG=1``         print the spec, the chosen kernel and the skip table at compile/call time.
+One flag of this package's own:
+  ``LF_CHECK_STATUS=1``  (also implied by ``DEBUG=1``) pass a device status word to every launch
+                      and read it back after the call (a synchronisation): a bounded device-side
+                      wait that ran out, or a block-table entry outside the pool, raises instead
+                      of returning a plausible tensor. Without the flag the word is not read.
 """
 from __future__ import annotations
 
@@ -50,7 +55,15 @@ class AttentionPlan:
     mods: tuple
     window: int = 0
     page_size: int = 0
-    skip_ranges: Optional[list] = None   # per q-tile (lo, hi) in KV tiles of TILE_K (prefill)
+    mask_kind: int = MASK_NONE
+
+    @property
+    def skip_ranges(self) -> Optional[list]:
+        """Per q-tile (lo, hi) in KV tiles of TILE_K (prefill kernels only); built on demand -
+        the kernels derive the same integers themselves."""
+        if self.kernel in ("decode", "paged_decode"):
+            return None
+        return skip_table(self.mask_kind, self.window, 0, self.Sq, self.Skv)
 
     def describe(self) -> str:
         s = (f"{self.kernel}: B={self.B} Hq={self.Hq} Hkv={self.Hkv} Sq={self.Sq} "
@@ -74,6 +87,10 @@ class CompiledAttention:
         self.workspace = F.DecodeWorkspace()
         self.analysis_only = _flag("CODEGEN_ONLY")
         self.debug = _flag("DEBUG")
+        self.check_status = self.debug or _flag("LF_CHECK_STATUS")
+        self._plans: dict = {}
+        self._prepared: dict = {}
+        self._status: dict = {}
 
     # -- binding -------------------------------------------------------------------------
     def _resolve_mods(self, flat_args: list) -> tuple[float, tuple]:
@@ -90,6 +107,17 @@ class CompiledAttention:
         return scale, tuple(mods)
 
     def plan(self, flat_args: list) -> AttentionPlan:
+        """The plan for this call's sizes; cached per (shapes, integer arguments)."""
+        key = tuple(a.shape if isinstance(a, torch.Tensor) else a for a in flat_args)
+        plan = self._plans.get(key)
+        if plan is None:
+            plan = self._make_plan(flat_args)
+            if len(self._plans) >= 64:
+                self._plans.clear()
+            self._plans[key] = plan
+        return plan
+
+    def _make_plan(self, flat_args: list) -> AttentionPlan:
         spec = self.spec
         q = flat_args[spec.q]
         if q.dim() != 4:
@@ -105,6 +133,9 @@ class CompiledAttention:
             k = flat_args[spec.k.placeholder]
             page_size = 0
             Hkv, Skv = k.shape[1], k.shape[2]
+        if spec.v.paged and not spec.k.paged:
+            vpool = flat_args[spec.v.placeholder]
+            page_size = vpool.shape[1] if vpool.dim() == 4 else 1
         if spec.k.repeated:
             if Hq % Hkv:
                 raise ValueError(f"repeat_interleave: Hq={Hq} is not a multiple of Hkv={Hkv}")
@@ -120,18 +151,41 @@ class CompiledAttention:
 
         group = Hq // Hkv
         decode_rows = Sq * group
+        both_paged = spec.k.paged and spec.v.paged
         is_decode = (spec.mask_kind == MASK_NONE and decode_rows in _DECODE_GROUPS
-                     and (Sq == 1 or group == 1))
-        ranges = None
+                     and (Sq == 1 or group == 1) and (both_paged or not
+                                                      (spec.k.paged or spec.v.paged)))
         if is_decode:
-            kernel = "paged_decode" if spec.k.paged else "decode"
+            kernel = "paged_decode" if both_paged else "decode"
         else:
-            kernel = "paged_gather+prefill" if spec.k.paged else "prefill"
-            ranges = skip_table(spec.mask_kind, window, 0, Sq, Skv)
+            kernel = "paged_gather+prefill" if (spec.k.paged or spec.v.paged) else "prefill"
         return AttentionPlan(spec, kernel, B, Hq, Hkv, Sq, Skv, D, scale, mods, window, page_size,
-                             ranges)
+                             spec.mask_kind)
 
     # -- launch --------------------------------------------------------------------------
+    def _status_for(self, device) -> Optional[torch.Tensor]:
+        if not self.check_status:
+            return None
+        st = self._status.get(device)
+        if st is None:
+            st = self._status[device] = F.new_status(device)
+        return st
+
+    def _prepared_prefill(self, plan: AttentionPlan, q, k, v, status) -> "F.PreparedPrefill":
+        """Prefill launches bound to (buffers, plan): a loop that calls the compiled function on
+        the same buffers pays the argument marshalling once."""
+        key = (q.data_ptr(), k.data_ptr(), v.data_ptr(), q.shape, k.shape, q.stride(),
+               k.stride(), v.stride(), id(plan))
+        prep = self._prepared.get(key)
+        if prep is None:
+            if len(self._prepared) >= 16:
+                self._prepared.clear()
+            prep = F.PreparedPrefill(q, k, v, scale=plan.scale, mods=plan.mods,
+                                     mask_kind=plan.mask_kind, window=plan.window,
+                                     status=status)
+            self._prepared[key] = prep
+        return prep
+
     def __call__(self, *flat_args: Any):
         args = list(flat_args)
         plan = self.plan(args)
@@ -141,6 +195,7 @@ class CompiledAttention:
             return (plan,)
         spec = self.spec
         q = args[spec.q]
+        status = self._status_for(q.device)
         if plan.kernel in ("decode", "paged_decode"):
             # G query rows per kv head: either Sq rows of one head (the reference's
             # [B, Hkv, g, D] convention, tests/benchmark.py:438-443) or the g heads that
@@ -159,22 +214,43 @@ class CompiledAttention:
             if plan.kernel == "decode":
                 F.decode_attention(q4, args[spec.k.placeholder], args[spec.v.placeholder],
                                    scale=plan.scale, mods=plan.mods, out=o4,
-                                   workspace=self.workspace)
+                                   workspace=self.workspace, status=status)
             else:
                 kt, vt = args[spec.k.block_table], args[spec.v.block_table]
                 F.paged_decode_attention(
                     q4, args[spec.k.placeholder], args[spec.v.placeholder], kt,
                     block_table_v=None if spec.v.block_table == spec.k.block_table else vt,
-                    scale=plan.scale, mods=plan.mods, out=o4, workspace=self.workspace)
+                    scale=plan.scale, mods=plan.mods, out=o4, workspace=self.workspace,
+                    status=status)
+            self._check(status, plan)
             return (out,)
-        if plan.kernel == "paged_gather+prefill":
-            k = F.paged_gather(args[spec.k.placeholder], args[spec.k.block_table])
-            v = F.paged_gather(args[spec.v.placeholder], args[spec.v.block_table])
+        # Prefill. A paged operand is gathered into a dense [B, Hkv, S, D] tensor first (the
+        # gather kernel applies the same page-index rule as the decode kernels); K and V may be
+        # paged independently, as in the reference's own paged-attention tests
+        # (tests/test_accuracy.py:253-311: K through paged_load, V dense).
+        if spec.k.paged:
+            k = F.paged_gather(args[spec.k.placeholder], args[spec.k.block_table], status=status)
         else:
-            k, v = args[spec.k.placeholder], args[spec.v.placeholder]
-        out = F.prefill_attention(q, k, v, scale=plan.scale, mods=plan.mods,
-                                  mask_kind=spec.mask_kind, window=plan.window)
+            k = args[spec.k.placeholder]
+        if spec.v.paged:
+            v = F.paged_gather(args[spec.v.placeholder], args[spec.v.block_table], status=status)
+        else:
+            v = args[spec.v.placeholder]
+        if spec.k.paged or spec.v.paged:
+            out = F.prefill_attention(q, k, v, scale=plan.scale, mods=plan.mods,
+                                      mask_kind=spec.mask_kind, window=plan.window, status=status)
+        else:
+            out = torch.empty((plan.B, plan.Hq, plan.Sq, plan.D), dtype=q.dtype, device=q.device)
+            self._prepared_prefill(plan, q, k, v, status).run(out)
+        self._check(status, plan)
         return (out,)
+
+    def _check(self, status: Optional[torch.Tensor], plan: AttentionPlan) -> None:
+        if status is not None:
+            try:
+                F.check_status(status, plan.kernel)
+            finally:
+                status.zero_()
 
 
 def loopfuse_compiler(gm: torch.fx.GraphModule, sample_inputs, mode: Optional[str] = None,

@@ -18,8 +18,19 @@ CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "liblf_sm100.so"
 STAMP_PATH = PKG_DIR / "csrc" / ".build_stamp"
 
-SOURCES = ["lf_api.cu", "lf_decode.cu", "lf_prefill.cu"]
-HEADERS = ["lf_common.cuh", "lf_skip_range.h", "../../include/lf_sm100.h"]
+PUBLIC_HEADER = PKG_DIR.parent / "include" / "lf_sm100.h"
+
+
+def _sources() -> list[Path]:
+    """Every translation unit under csrc/."""
+    return sorted(CSRC.glob("*.cu"))
+
+
+def fingerprint_files() -> list[Path]:
+    """Everything the library is built from: all .cu / .cuh / .h files under csrc/ and the
+    public header. A change to any of them forces a rebuild."""
+    files = set(CSRC.glob("*.cu")) | set(CSRC.glob("*.cuh")) | set(CSRC.glob("*.h"))
+    return sorted(files) + [PUBLIC_HEADER]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -37,15 +48,11 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc not found: cannot build liblf_sm100.so")
 
 
-def _existing_sources() -> list[str]:
-    return [s for s in SOURCES if (CSRC / s).exists()]
-
-
 def _fingerprint() -> str:
     h = hashlib.sha256()
-    for name in _existing_sources() + HEADERS:
-        h.update(name.encode())
-        h.update((CSRC / name).read_bytes())
+    for path in fingerprint_files():
+        h.update(path.name.encode())
+        h.update(path.read_bytes())
     h.update(" ".join(NVCC_FLAGS).encode())
     return h.hexdigest()
 
@@ -59,9 +66,10 @@ def build_native(force: bool = False, verbose: bool = False) -> Path:
     objs = []
     log = []
     procs = []
-    for src in _existing_sources():
-        obj = CSRC / (src[:-3] + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-c", str(CSRC / src), "-o", str(obj)]
+    for path in _sources():
+        src = path.name
+        obj = path.with_suffix(".o")
+        cmd = [nvcc, *NVCC_FLAGS, "-c", str(path), "-o", str(obj)]
         procs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE,
                                                  stderr=subprocess.STDOUT, text=True)))
     for src, obj, proc in procs:

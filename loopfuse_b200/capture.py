@@ -250,8 +250,6 @@ class _Matcher:
         q_idx = self._tensor_placeholder(q_node, "Q")
         if k_src.repeated != v_src.repeated:
             raise NotImplementedError("K and V must both (or neither) be repeat_interleave'd")
-        if k_src.paged != v_src.paged:
-            raise NotImplementedError("K and V must both be dense or both be paged")
 
         for idx, what in ((q_idx, "Q"), (k_src.placeholder, "K"), (v_src.placeholder, "V")):
             dt = self.placeholders[idx].meta["val"].dtype

@@ -724,26 +724,62 @@ static int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
 static bool uses_mma_kernel(int G, bool paged) { return paged || G > 2; }
 
-static int choose_splits(int B, int Hkv, int G, int Skv, int D, bool paged) {
+// Shared memory the tensor-core kernel may spend on block-table slices (both tables), so that
+// two CTAs (K/V rings of 96 KB each at D = 128) still fit on one SM.
+constexpr size_t kMaxTableBytes = 16 * 1024;
+
+static size_t table_smem_bytes(int chunk, int page_size) {
+  // Room for the K table and a separate V table, each padded to 16 bytes.
+  return 2 * (((static_cast<size_t>(chunk / page_size) + 2 + 3) & ~size_t(3)) * 4);
+}
+
+// Largest token chunk of one split whose block-table slice fits (paged caches only).
+static int max_chunk_for_table(int page_size) {
+  const int entries = static_cast<int>(kMaxTableBytes / 8) - 4;  // per table, minus padding
+  const int64_t tokens = static_cast<int64_t>(entries) * page_size;
+  return static_cast<int>(tokens > (1 << 30) ? (1 << 30) : tokens / 64 * 64);
+}
+
+// Split count for splits == 0. page_size: 0 for a dense cache, else the tokens per page.
+static int choose_splits(int B, int Hkv, int G, int Skv, int D, int page_size) {
   (void)D;
+  const bool paged = page_size > 0;
   const int units = B * Hkv;
   const int sms = device_sm_count();
   int max_by_len = Skv / 256;  // keep >= 256 tokens per split
   if (max_by_len < 1) max_by_len = 1;
+  if (max_by_len > 32) max_by_len = 32;
   int s;
   if (uses_mma_kernel(G, paged)) {
     // Two CTAs of the tensor-core kernel are resident per SM and each keeps ~16 KB in flight
-    // per warp, so one wave already saturates HBM: split only to fill the machine (splitting
-    // costs the partial round trip and a short, badly pipelined loop per CTA).
+    // per warp, so one full wave saturates HBM. Splitting costs the partial round trip and a
+    // shorter loop per CTA, so split only as far as the last wave needs: take the smallest
+    // split count whose CTA count fills at least 95 % of its last wave (512 units on 296 slots
+    // are 1.73 waves unsplit, 6.92 waves split four ways).
     const int resident = sms * 2;
-    s = units >= resident ? 1 : (resident + units - 1) / units;
+    s = 1;
+    double best = 0.0;
+    for (int cand = 1; cand <= max_by_len; ++cand) {
+      const double waves = static_cast<double>(units) * cand / resident;
+      const double eff = waves / static_cast<double>(static_cast<int64_t>(waves + 0.999999));
+      if (eff > best + 1e-9) {
+        best = eff;
+        s = cand;
+      }
+      if (eff >= 0.95) break;
+    }
   } else {
     // The FMA kernel has ~8 small CTAs per SM: aim for >= 6 waves so the tail wave is cheap.
     s = (sms * 8 * 6 + units - 1) / units;
   }
   if (s > max_by_len) s = max_by_len;
   if (s < 1) s = 1;
-  if (s > 32) s = 32;
+  if (paged) {
+    // The block-table slice of a split must fit in shared memory (one-token pages at long
+    // context): split further until it does.
+    const int max_chunk = max_chunk_for_table(page_size);
+    while (s < 32 && round_up((Skv + s - 1) / s, 64) > max_chunk) ++s;
+  }
   return s;
 }
 
@@ -821,7 +857,8 @@ static int decode_impl(const LfDecodeArgs* a, void* stream, bool paged) {
   int splits = a->splits;
   if (splits < 0) return LF_ERR_INVALID_ARG;
   if (splits > 32) return LF_ERR_TOO_LARGE;
-  if (splits == 0) splits = choose_splits(a->B, a->Hkv, a->G, a->Skv, a->D, paged);
+  if (splits == 0)
+    splits = choose_splits(a->B, a->Hkv, a->G, a->Skv, a->D, paged ? a->page_size : 0);
   // Token chunk per split: a multiple of 64 (and of the page size when that is a power of
   // two up to 64), so a split never starts in the middle of a warp's token batch.
   int chunk = round_up((a->Skv + splits - 1) / splits, 64);
@@ -869,8 +906,16 @@ static int decode_impl(const LfDecodeArgs* a, void* stream, bool paged) {
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   size_t smem = static_cast<size_t>(kDecodeWarps) * a->G * (a->D + 2) * sizeof(float);
-  if (paged) smem += 2 * (((static_cast<size_t>(chunk / p.page_size) + 2 + 3) & ~size_t(3)) * 4);
-  if (smem > 48 * 1024) return LF_ERR_TOO_LARGE;
+  if (paged) {
+    // A split's block-table slice lives in shared memory next to the K/V rings. The automatic
+    // split count already keeps it small enough; an explicit count that does not is refused
+    // (pass a larger `splits`, or 0).
+    const size_t table_bytes = table_smem_bytes(chunk, p.page_size);
+    if (table_bytes > kMaxTableBytes) return LF_ERR_TOO_LARGE;
+    smem += table_bytes;
+  } else if (smem > 48 * 1024) {
+    return LF_ERR_TOO_LARGE;
+  }
 
   int rc;
   if (a->D == 128)
@@ -893,7 +938,7 @@ extern "C" {
 int lf_decode_auto_splits(int32_t B, int32_t Hkv, int32_t G, int32_t Skv, int32_t D,
                           int32_t paged) {
   if (B <= 0 || Hkv <= 0 || Skv <= 0) return 1;
-  int splits = lf::choose_splits(B, Hkv, G, Skv, D, paged != 0);
+  int splits = lf::choose_splits(B, Hkv, G, Skv, D, paged > 0 ? paged : 0);
   const int chunk = lf::round_up((Skv + splits - 1) / splits, 64);
   return (Skv + chunk - 1) / chunk;
 }
@@ -1017,7 +1062,7 @@ extern "C" int lf_decode_bf16_static(const LfDecodeArgs* args, void* stream) {
   int splits = args->splits;
   if (splits < 0) return LF_ERR_INVALID_ARG;
   if (splits == 0)
-    splits = lf::choose_splits(args->B, args->Hkv, args->G, args->Skv, args->D, false);
+    splits = lf::choose_splits(args->B, args->Hkv, args->G, args->Skv, args->D, 0);
   const int chunk = lf::round_up((args->Skv + splits - 1) / splits, 64);
   splits = (args->Skv + chunk - 1) / chunk;
   const size_t need = lf_decode_workspace_bytes(args->B, args->Hkv, args->G, args->D, splits);

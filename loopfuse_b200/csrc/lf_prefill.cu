@@ -108,34 +108,6 @@ struct __align__(8) PrefillBarriers {
   uint32_t pad;
 };
 
-// Optional phase tracing (compiled in only with -DLF_TRACE): the first CTA's role threads log
-// (event id, SM clock) pairs into `dbg_ranges`, which then must hold 4 * 2048 int64 values.
-#ifdef LF_TRACE
-struct Tracer {
-  long long* buf;
-  int n;
-  __device__ __forceinline__ void ev(int id) {
-    if (buf && n < 1023) {
-      buf[2 * n] = id;
-      buf[2 * n + 1] = clock64();
-      ++n;
-    }
-  }
-};
-#define LF_TRACE_DECL(role, cond)                                                             \
-  Tracer tracer{(blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && p.dbg_ranges &&     \
-                 (cond))                                                                      \
-                    ? reinterpret_cast<long long*>(p.dbg_ranges) + (role) * 2048              \
-                    : nullptr,                                                                \
-                0}
-#define LF_TRACE_EV(id) tracer.ev(id)
-#define LF_TRACE_END() do { if (tracer.buf) { tracer.buf[2 * tracer.n] = -1; } } while (0)
-#else
-#define LF_TRACE_DECL(role, cond)
-#define LF_TRACE_EV(id)
-#define LF_TRACE_END()
-#endif
-
 __device__ __forceinline__ void report_timeout(int32_t* status, int where) {
   if (status) atomicCAS(status, LF_DEV_OK, LF_DEV_TIMEOUT | (where << 8));
 }
@@ -230,7 +202,6 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
   if (warp == kProducerWarp) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      LF_TRACE_DECL(3, true);
       for (int t = 0; t < 2; ++t) {
         if (!has_work[t]) continue;
         mbar_arrive_expect_tx(&bars->q_full[t], kQTileBytes);
@@ -249,13 +220,11 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         const int stage = n % kStages;
         const uint32_t parity = ((n / kStages) & 1) ^ 1;
         ++n;
-        LF_TRACE_EV(1);
         if (!mbar_wait(&bars->kv_empty[stage], parity)) {
           report_timeout(p.status, 1);
           ok = false;
           return;
         }
-        LF_TRACE_EV(2);
         mbar_arrive_expect_tx(&bars->kv_full[stage], jb >= 0 ? 2 * kKVTileBytes : kKVTileBytes);
         unsigned char* dst = sKV + stage * (2 * kKVTileBytes);
 #pragma unroll
@@ -273,7 +242,6 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         load_pair(&tmap_k, lo, lo + 1 < hi ? lo + 1 : -1);
         for (int j = lo; j < hi; ++j) load_pair(&tmap_v, j, j + 2 < hi ? j + 2 : -1);
       }
-      LF_TRACE_END();
     }
   } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
     // ---------------- MMA issuers: one warp per query tile ----------
@@ -283,8 +251,6 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     if (lane == 0 && hi > lo) {
       const int t = warp - kMmaWarp0;
       bool ok = true;
-      LF_TRACE_DECL(2, t == 0);
-      LF_TRACE_EV(0);
       if (has_work[t] && !mbar_wait(&bars->q_full[t], 0)) {
         report_timeout(p.status, 2);
         ok = false;
@@ -347,11 +313,9 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       }
       const int nblk_t = has_work[t] ? hi_t[t] - lo_t[t] : 0;
       for (int j = lo; j < hi && ok; ++j) {
-        LF_TRACE_EV(10);
         const int st = wait_stage(4);  // {V(j), K(j+2)}
         if (st < 0) break;
         tc_fence_after();
-        LF_TRACE_EV(11);
         if (active(j)) {
           const int kt = j - lo_t[t];
           if (!mbar_wait(&bars->p_full[t][kt & 1], (kt >> 1) & 1)) {
@@ -360,9 +324,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
             break;
           }
           tc_fence_after();
-          LF_TRACE_EV(13);
           issue_pv(st, kt);
-          LF_TRACE_EV(14);
           // Completion points the softmax warps may wait on: the second-to-last PV (for a
           // rescale in the last block) and the last PV (for the epilogue).
           if (kt == nblk_t - 2) tc_commit(&bars->pv_done[t]);
@@ -370,9 +332,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         }
         if (j + 2 < hi && active(j + 2)) issue_qk(st, 1, j + 2);
         tc_commit(&bars->kv_empty[st]);
-        LF_TRACE_EV(15);
       }
-      LF_TRACE_END();
     }
   } else {
     // ---------------- softmax warps ----------------
@@ -383,13 +343,11 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     const uint32_t s_base = tmem_base + lane_addr + t * 128;
     const uint32_t o_addr = tmem_base + lane_addr + kColO + t * 128;
 
-#ifndef LF_TRACE
     if (p.dbg_ranges && tile_valid[t] && row == 0) {
       const int64_t idx = ((static_cast<int64_t>(b) * p.Hq + h) * p.n_qtiles + (iq0 + t)) * 2;
       p.dbg_ranges[idx] = lo_t[t];
       p.dbg_ranges[idx + 1] = hi_t[t];
     }
-#endif
 
     if (has_work[t]) {
       // Visible column interval of this row: [c_lo, c_hi].
@@ -403,19 +361,16 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       float l_run = 0.f;
       bool ok = true;
       const int nblk = hi_t[t] - lo_t[t];
-      LF_TRACE_DECL(t, (warp & 3) == 0 && lane == 0);
       for (int k = 0; k < nblk; ++k) {
         const int c0 = (lo_t[t] + k) * kTileK;
         const int buf = k & 1;
         const uint32_t s_addr = s_base + buf * 64;
-        LF_TRACE_EV(20);
         if (!mbar_wait(&bars->s_full[t][buf], (k >> 1) & 1)) {
           report_timeout(p.status, 8 + t);
           ok = false;
           break;
         }
         tc_fence_after();
-        LF_TRACE_EV(21);
         // Raw scores of this row: 64 fp32 values.
         uint32_t sr[2][32];
         tmem_ld_32x32b_x32(s_addr, sr[0]);
@@ -467,7 +422,6 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
           }
           mx_keep = fmaxf(mxa[0], mxa[1]);
         }
-        LF_TRACE_EV(22);
 
         // The score function is monotonic for the plain and softcap modes, so the max of the
         // scores is the score of the max.
@@ -517,7 +471,6 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
           }
         }
         const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-        LF_TRACE_EV(23);
 
         // Pass 2: p = exp2(score * c2 - m), two elements per packed instruction.
         const uint64_t neg_m2 = pack2(-m_safe, -m_safe);
@@ -631,14 +584,11 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         for (int c = 0; c < 4; ++c) unpack2(psum2[c], ps[2 * c], ps[2 * c + 1]);
         const float psum = ((ps[0] + ps[1]) + (ps[2] + ps[3])) + ((ps[4] + ps[5]) + (ps[6] + ps[7]));
         l_run = l_run * alpha + psum;
-        LF_TRACE_EV(24);
         tmem_st_32x32b_x32(s_addr, pk);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&bars->p_full[t][buf]);
-        LF_TRACE_EV(25);
       }
-      LF_TRACE_EV(26);
 
       // Epilogue: O_t / l -> bf16 -> global (one row per thread).
       if (ok) {
@@ -688,8 +638,6 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
           __syncwarp();
         }
       }
-      LF_TRACE_EV(27);
-      LF_TRACE_END();
     } else if (tile_valid[t] && grow < p.Sq) {
       // No visible key at all for this tile: softmax of an all -inf row is NaN in the
       // eager computation, so the rows are written as NaN.
@@ -713,6 +661,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
 }  // namespace lf
 
 #include "lf_prefill_bounded.cuh"
+#include "lf_prefill_wide.cuh"
 
 namespace lf {
 
@@ -737,10 +686,10 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
 
 // Tensor map over a bf16 [B, H, S, D] tensor (innermost stride 1), box = [1, 1, box_rows,
 // box_cols]; 128-byte swizzle for 64-column boxes (the K/V/Q loads, out-of-range rows read as
-// zero), 64-byte swizzle for 32-column boxes (the output store of the persistent kernel).
-static int make_tile_map(CUtensorMap* map, const void* base, int B, int H, int S, int D,
-                         const int64_t* stride /* b, h, s in elements */, int box_rows,
-                         int box_cols = 64) {
+// zero), 64-byte swizzle for 32-column boxes (the output store of the persistent kernels).
+static int encode_tile_map(CUtensorMap* map, const void* base, int B, int H, int S, int D,
+                           const int64_t* stride /* b, h, s in elements */, int box_rows,
+                           int box_cols) {
   auto fn = get_encode_fn();
   if (!fn) return LF_ERR_CUDA;
   cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S),
@@ -766,6 +715,60 @@ static int make_tile_map(CUtensorMap* map, const void* base, int B, int H, int S
     set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
     return LF_ERR_CUDA;
   }
+  return LF_OK;
+}
+
+// Encoded tensor maps are kept in a small cache: a map depends only on (address, shape,
+// strides, box), and serving loops call with the same buffers again and again. Direct-mapped,
+// one mutex; a miss just encodes again, so the cache never changes a result. A CUtensorMap holds
+// no reference to the memory it describes: an entry whose buffer was freed is harmless and is
+// simply replaced when another key lands on its slot.
+struct TileMapKey {
+  const void* base;
+  int32_t B, H, S, D, box_rows, box_cols;
+  int64_t stride[3];
+  bool operator==(const TileMapKey& o) const {
+    return base == o.base && B == o.B && H == o.H && S == o.S && D == o.D &&
+           box_rows == o.box_rows && box_cols == o.box_cols && stride[0] == o.stride[0] &&
+           stride[1] == o.stride[1] && stride[2] == o.stride[2];
+  }
+};
+struct TileMapEntry {
+  bool valid = false;
+  TileMapKey key;
+  CUtensorMap map;
+};
+constexpr int kTileMapCacheSlots = 256;
+static std::mutex g_tile_map_mutex;
+static TileMapEntry g_tile_map_cache[kTileMapCacheSlots];
+static std::atomic<uint64_t> g_tile_map_hits{0}, g_tile_map_misses{0};
+
+static int make_tile_map(CUtensorMap* map, const void* base, int B, int H, int S, int D,
+                         const int64_t* stride, int box_rows, int box_cols = 64) {
+  TileMapKey key{base, B, H, S, D, box_rows, box_cols, {stride[0], stride[1], stride[2]}};
+  uint64_t h = reinterpret_cast<uintptr_t>(base) * 0x9E3779B97F4A7C15ull;
+  h ^= (static_cast<uint64_t>(S) << 32 | static_cast<uint32_t>(H)) * 0xC2B2AE3D27D4EB4Full;
+  h ^= (static_cast<uint64_t>(B) << 40 | static_cast<uint64_t>(box_rows) << 16 |
+        static_cast<uint64_t>(box_cols) << 8 | static_cast<uint64_t>(D)) * 0x165667B19E3779F9ull;
+  h ^= static_cast<uint64_t>(stride[2]) * 0x27D4EB2F165667C5ull;
+  const int slot = static_cast<int>((h >> 32) % kTileMapCacheSlots);
+  {
+    std::lock_guard<std::mutex> lock(g_tile_map_mutex);
+    const TileMapEntry& e = g_tile_map_cache[slot];
+    if (e.valid && e.key == key) {
+      *map = e.map;
+      g_tile_map_hits.fetch_add(1, std::memory_order_relaxed);
+      return LF_OK;
+    }
+  }
+  const int rc = encode_tile_map(map, base, B, H, S, D, stride, box_rows, box_cols);
+  if (rc != LF_OK) return rc;
+  g_tile_map_misses.fetch_add(1, std::memory_order_relaxed);
+  std::lock_guard<std::mutex> lock(g_tile_map_mutex);
+  TileMapEntry& e = g_tile_map_cache[slot];
+  e.key = key;
+  e.map = *map;
+  e.valid = true;
   return LF_OK;
 }
 
@@ -801,6 +804,7 @@ static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CU
 // overlap on the GPU use different slots unless more than kTicketSlots are in flight.
 constexpr int kTicketSlots = 256;
 static __device__ unsigned int g_prefill_tickets[kTicketSlots];
+static std::atomic<unsigned int> g_next_ticket_slot{0};
 
 template <int D>
 static int launch_prefill_bounded(const CUtensorMap& mq, const CUtensorMap& mk,
@@ -813,7 +817,6 @@ static int launch_prefill_bounded(const CUtensorMap& mq, const CUtensorMap& mk,
   static thread_local int configured_dev = -1;
   static thread_local unsigned int* tickets = nullptr;
   static thread_local int sm_count = 0;
-  static std::atomic<unsigned int> next_slot{0};
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_dev != dev) {
@@ -833,7 +836,7 @@ static int launch_prefill_bounded(const CUtensorMap& mq, const CUtensorMap& mk,
   const int64_t n_items = static_cast<int64_t>(p.n_pairs) * p.Hq * B;
   if (n_items > 0x7fffffff - 4096) return LF_ERR_TOO_LARGE;
   p.n_items = static_cast<int32_t>(n_items);
-  p.ticket = tickets + next_slot.fetch_add(1) % kTicketSlots;
+  p.ticket = tickets + g_next_ticket_slot.fetch_add(1) % kTicketSlots;
   cudaError_t e = cudaMemsetAsync(p.ticket, 0, sizeof(unsigned int), st);
   if (e != cudaSuccess) {
     set_cuda_error(e, "cudaMemsetAsync(ticket)");
@@ -844,7 +847,60 @@ static int launch_prefill_bounded(const CUtensorMap& mq, const CUtensorMap& mk,
   return check_launch("prefill_bounded_kernel");
 }
 
-static int prefill_impl(const LfPrefillArgs* a, void* stream) {
+template <int D>
+static int launch_prefill_wide(const CUtensorMap& mq, const CUtensorMap& mk,
+                               const CUtensorMap& mv, const CUtensorMap& mo, PrefillParams p,
+                               int B, cudaStream_t st) {
+  constexpr size_t kQTileBytes = static_cast<size_t>(kTileQ) * D * 2;
+  constexpr size_t kKVTileBytes = static_cast<size_t>(kWideK) * D * 2;
+  constexpr size_t smem = 1024 /*align slack*/ + 1024 /*barriers*/ + kBoundedStageBytes +
+                          2 * kQTileBytes + WideRingFor<D>::value * kKVTileBytes;
+  static thread_local int configured_dev = -1;
+  static thread_local unsigned int* tickets = nullptr;
+  static thread_local int sm_count = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_dev != dev) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_wide_kernel<D>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e == cudaSuccess)
+      e = cudaGetSymbolAddress(reinterpret_cast<void**>(&tickets), g_prefill_tickets);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) {
+      set_cuda_error(e, "prefill_wide_kernel setup");
+      return LF_ERR_CUDA;
+    }
+    configured_dev = dev;
+  }
+  p.n_pairs = (p.n_qtiles + 1) / 2;
+  const int64_t n_items = static_cast<int64_t>(p.n_pairs) * p.Hq * B;
+  if (n_items > 0x7fffffff - 4096) return LF_ERR_TOO_LARGE;
+  p.n_items = static_cast<int32_t>(n_items);
+  p.ticket = tickets + g_next_ticket_slot.fetch_add(1) % kTicketSlots;
+  cudaError_t e = cudaMemsetAsync(p.ticket, 0, sizeof(unsigned int), st);
+  if (e != cudaSuccess) {
+    set_cuda_error(e, "cudaMemsetAsync(ticket)");
+    return LF_ERR_CUDA;
+  }
+  const int grid = static_cast<int>(n_items < sm_count ? n_items : sm_count);
+  prefill_wide_kernel<D><<<grid, kWideThreads, smem, st>>>(mq, mk, mv, mo, p);
+  return check_launch("prefill_wide_kernel");
+}
+
+// KV tile of the kernel that serves these arguments: 128 keys for the bounded-softcap kernel
+// unless the caller pins 64 (or the window is so short that 128-key blocks would be mostly
+// masked), 64 keys for every running-max kernel.
+static int choose_kv_tile(const LfPrefillArgs* a, int mode) {
+  if (a->kv_tile != 0 && a->kv_tile != kTileK && a->kv_tile != kWideK) return LF_ERR_INVALID_ARG;
+  if (mode != kModeBounded) return a->kv_tile == kWideK ? LF_ERR_UNSUPPORTED : kTileK;
+  if (a->kv_tile != 0) return a->kv_tile;
+  if (a->mask_kind == LF_MASK_CAUSAL_WINDOW && a->window < kWideK) return kTileK;
+  return kWideK;
+}
+
+// `launch` == nullptr: only resolve the kernel choice and return its KV tile size.
+static int prefill_impl(const LfPrefillArgs* a, void* const* launch) {
   if (!a || !a->q || !a->k || !a->v || !a->out) return LF_ERR_INVALID_ARG;
   if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Sq <= 0 || a->Skv <= 0)
     return LF_ERR_INVALID_ARG;
@@ -934,30 +990,38 @@ static int prefill_impl(const LfPrefillArgs* a, void* stream) {
     }
   }
 
+  const int kv_tile = choose_kv_tile(a, mode);
+  if (kv_tile < 0) return kv_tile;
+  if (launch == nullptr) return kv_tile;  // query only
+
   CUtensorMap mq, mk, mv;
   int rc = make_tile_map(&mq, a->q, a->B, a->Hq, a->Sq, a->D, a->q_stride, kTileQ);
   if (rc != LF_OK) return rc;
-  rc = make_tile_map(&mk, a->k, a->B, a->Hkv, a->Skv, a->D, a->k_stride, kTileK);
+  rc = make_tile_map(&mk, a->k, a->B, a->Hkv, a->Skv, a->D, a->k_stride, kv_tile);
   if (rc != LF_OK) return rc;
-  rc = make_tile_map(&mv, a->v, a->B, a->Hkv, a->Skv, a->D, a->v_stride, kTileK);
+  rc = make_tile_map(&mv, a->v, a->B, a->Hkv, a->Skv, a->D, a->v_stride, kv_tile);
   if (rc != LF_OK) return rc;
 
-  CUtensorMap mo;  // output store boxes of the persistent kernel: 32 rows x 32 columns
+  CUtensorMap mo;  // output store boxes of the persistent kernels: 32 rows x 32 columns
   if (mode == kModeBounded) {
     rc = make_tile_map(&mo, a->out, a->B, a->Hq, a->Sq, a->D, a->o_stride, 32, 32);
     if (rc != LF_OK) return rc;
   }
 
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaStream_t st = static_cast<cudaStream_t>(*launch);
   if (a->D == 128) {
     if (mode == kModeNone) return launch_prefill<128, kModeNone>(mq, mk, mv, p, a->B, st);
     if (mode == kModeSoftcap) return launch_prefill<128, kModeSoftcap>(mq, mk, mv, p, a->B, st);
-    if (mode == kModeBounded) return launch_prefill_bounded<128>(mq, mk, mv, mo, p, a->B, st);
+    if (mode == kModeBounded)
+      return kv_tile == kWideK ? launch_prefill_wide<128>(mq, mk, mv, mo, p, a->B, st)
+                               : launch_prefill_bounded<128>(mq, mk, mv, mo, p, a->B, st);
     return launch_prefill<128, kModeGeneric>(mq, mk, mv, p, a->B, st);
   }
   if (mode == kModeNone) return launch_prefill<64, kModeNone>(mq, mk, mv, p, a->B, st);
   if (mode == kModeSoftcap) return launch_prefill<64, kModeSoftcap>(mq, mk, mv, p, a->B, st);
-  if (mode == kModeBounded) return launch_prefill_bounded<64>(mq, mk, mv, mo, p, a->B, st);
+  if (mode == kModeBounded)
+    return kv_tile == kWideK ? launch_prefill_wide<64>(mq, mk, mv, mo, p, a->B, st)
+                             : launch_prefill_bounded<64>(mq, mk, mv, mo, p, a->B, st);
   return launch_prefill<64, kModeGeneric>(mq, mk, mv, p, a->B, st);
 }
 
@@ -966,7 +1030,14 @@ static int prefill_impl(const LfPrefillArgs* a, void* stream) {
 extern "C" {
 
 int lf_prefill_bf16(const LfPrefillArgs* args, void* stream) {
-  return lf::prefill_impl(args, stream);
+  return lf::prefill_impl(args, &stream);
+}
+
+int lf_prefill_kv_tile(const LfPrefillArgs* args) { return lf::prefill_impl(args, nullptr); }
+
+void lf_tile_map_cache_stats(uint64_t* hits, uint64_t* misses) {
+  if (hits) *hits = lf::g_tile_map_hits.load();
+  if (misses) *misses = lf::g_tile_map_misses.load();
 }
 
 void lf_skip_range(int32_t mask_kind, int32_t window, int32_t causal_offset, int32_t Sq,

@@ -68,7 +68,8 @@ struct ItemGeom {
   __device__ __forceinline__ int hi_t(int t) const { return t ? hi1 : hi0; }
 };
 
-__device__ __forceinline__ ItemGeom decode_item(const PrefillParams& p, int it) {
+__device__ __forceinline__ ItemGeom decode_item(const PrefillParams& p, int it,
+                                                int tile_k = kTileK) {
   ItemGeom g;
   g.it = it;
   const int pair = p.n_pairs - 1 - it % p.n_pairs;  // heaviest query tiles of a head first
@@ -77,9 +78,9 @@ __device__ __forceinline__ ItemGeom decode_item(const PrefillParams& p, int it) 
   g.b = hb / p.Hq;
   g.hkv = g.h / p.group;
   g.iq0 = pair * 2;
-  skip_range(p.mask_kind, p.window, p.causal_offset, p.Sq, p.Skv, kTileQ, kTileK, g.iq0, &g.lo0,
+  skip_range(p.mask_kind, p.window, p.causal_offset, p.Sq, p.Skv, kTileQ, tile_k, g.iq0, &g.lo0,
              &g.hi0);
-  skip_range(p.mask_kind, p.window, p.causal_offset, p.Sq, p.Skv, kTileQ, kTileK, g.iq0 + 1,
+  skip_range(p.mask_kind, p.window, p.causal_offset, p.Sq, p.Skv, kTileQ, tile_k, g.iq0 + 1,
              &g.lo1, &g.hi1);
   const bool v0 = g.iq0 * kTileQ < p.Sq, v1 = (g.iq0 + 1) * kTileQ < p.Sq;
   const bool w0 = v0 && g.hi0 > g.lo0, w1 = v1 && g.hi1 > g.lo1;
@@ -198,7 +199,6 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
   if (warp == kProducerWarp) {
     // ---------------- TMA producer (and item dispatcher) ----------------
     if (lane == 0) {
-      LF_TRACE_DECL(3, true);
       int n = 0;                // ring position, runs across items
       int qseq[2] = {0, 0};     // items with work so far, per tile
       bool ok = true;
@@ -207,13 +207,11 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
         const int stage = n % kStages;
         const uint32_t parity = ((n / kStages) & 1) ^ 1;
         ++n;
-        LF_TRACE_EV(1);
         if (!mbar_wait(&bars->kv_empty[stage], parity)) {
           report_timeout(p.status, 1);
           ok = false;
           return;
         }
-        LF_TRACE_EV(2);
         mbar_arrive_expect_tx(&bars->kv_full[stage], jb >= 0 ? 2 * kKVTileBytes : kKVTileBytes);
         unsigned char* dst = sKV + stage * (2 * kKVTileBytes);
 #pragma unroll
@@ -262,7 +260,6 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
             load_pair(&tmap_v, j, j + 2 < g.hi ? j + 2 : -1, g.hkv, g.b);
         }
       }
-      LF_TRACE_END();
     }
   } else if (warp >= kMmaWarp0 && warp < kMmaWarp0 + 4) {
     // ---------------- MMA issuers: a PV thread and a QK^T thread per query tile ----------
@@ -273,8 +270,6 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
       const int t = (warp - kMmaWarp0) & 1;
       const bool is_qk = warp - kMmaWarp0 >= 2;
       bool ok = true;
-      LF_TRACE_DECL(2, t == 0 && is_qk);
-      LF_TRACE_EV(0);
       constexpr uint32_t kStageUnits = (2 * kKVTileBytes) >> 4;  // a stage is a pair of tiles
       constexpr uint32_t kHalfUnits = kKVTileBytes >> 4;
       const uint32_t s_col = tmem_base + t * 128;
@@ -347,16 +342,13 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
             tc_commit(&bars->kv_empty[stage]);
           }
           for (int j = lo; j < hi && ok; ++j) {
-            LF_TRACE_EV(10);
             const int st = wait_stage(4);  // {V(j), K(j+2)}
             if (st < 0) break;
-            LF_TRACE_EV(11);
             if (j + 2 < hi && active(j + 2)) {
               tc_fence_after();
               if (!issue_qk(st, 1, j + 2)) break;
             }
             tc_commit(&bars->kv_empty[st]);
-            LF_TRACE_EV(15);
           }
         } else {
           {  // the first stage of an item holds K tiles only
@@ -400,7 +392,6 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
         }
         if (work) gblk += hi_tt - lo_tt;
       }
-      LF_TRACE_END();
     }
   } else {
     // ---------------- softmax warps ----------------
@@ -435,20 +426,16 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
     int wseq = 0;  // items with work for this tile so far
     bool ok = true;
     bool store_pending = false;  // an output store of this warp may still be reading `stage`
-    LF_TRACE_DECL(t, half == 0 && quarter == 0 && lane == 0);
     for (int seq = 0; ok; ++seq) {
       const ItemGeom g = next_item(seq, true);
-      LF_TRACE_EV(28);
       if (g.it < 0) break;
       const int grow = (g.iq0 + t) * kTileQ + row;
-#ifndef LF_TRACE
       if (p.dbg_ranges && g.valid(t) && row == 0 && half == 0) {
         const int64_t idx =
             ((static_cast<int64_t>(g.b) * p.Hq + g.h) * p.n_qtiles + (g.iq0 + t)) * 2;
         p.dbg_ranges[idx] = g.lo_t(t);
         p.dbg_ranges[idx + 1] = g.hi_t(t);
       }
-#endif
       if (!g.work(t)) {
         if (g.valid(t) && grow < p.Sq && half == 0) {
           // No visible key at all for this tile: softmax of an all -inf row is NaN in the
@@ -476,14 +463,12 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
         const int gk = gblk + k;
         const int buf = gk & 1;
         const uint32_t s_addr = s_base + buf * 64;
-        LF_TRACE_EV(20);
         if (!mbar_wait(&bars->s_full[t][buf], (gk >> 1) & 1)) {
           report_timeout(p.status, 8 + t);
           ok = false;
           break;
         }
         tc_fence_after();
-        LF_TRACE_EV(21);
         const int rel_lo = c_lo - c0;  // visible columns of this thread's 32: [rel_lo, rel_hi]
         const int rel_hi = c_hi - c0;
         // Warp-uniform decisions (the 32 x 32 piece of the block that this warp owns is fully
@@ -503,7 +488,6 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
           uint32_t sr[32];
           tmem_ld_32x32b_x32(s_addr, sr);
           tmem_wait_ld();
-          LF_TRACE_EV(22);
           float psum[4] = {0.f, 0.f, 0.f, 0.f};
           float ymax0 = 0.f, ymax1 = 0.f;
           auto finish_pair = [&](uint64_t z2, int i, bool apply_mask) {
@@ -570,7 +554,6 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
           if (!redo) break;
         }
         l_run += block_sum;
-        LF_TRACE_EV(24);
         // P (bf16, two per column) goes on top of the first 16 of this thread's S columns.
         tmem_st_32x32b_x16(s_addr, pk);
         tmem_wait_st();
@@ -582,15 +565,20 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
         // One arrival per warp (256 arrivals on one barrier word would serialise).
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->p_full[t][buf]);
-        LF_TRACE_EV(25);
       }
       if (!ok) break;
       gblk += nblk;
-      LF_TRACE_EV(26);
 
-      // Row sum: each thread leaves its half in the partner's staging buffer. (The partner's
-      // bulk store of the previous item has read that buffer: the partner checked it before its
-      // first P of this item, which every block of this item needed.)
+      // Row sum: each thread leaves its half in the partner's staging buffer. The partner's bulk
+      // store of the previous item must have read that buffer first: the partner confirmed that
+      // before its first P arrival of this item, so the completed P barrier of the item's last
+      // block (eight arrivals, the partner's included) orders this write after it. (Without this
+      // wait an item of one or two blocks gave no such ordering.)
+      if (!mbar_wait(&bars->p_full[t][(gblk - 1) & 1], ((gblk - 1) >> 1) & 1)) {
+        report_timeout(p.status, 16 + t);
+        ok = false;
+        break;
+      }
       *l_partner = l_run;
       mbar_arrive(&bars->l_ready[t]);
       if (!mbar_wait(&bars->l_ready[t], wseq & 1)) {
@@ -599,7 +587,6 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
         break;
       }
       l_run += *l_mine;
-      LF_TRACE_EV(30);
       // Epilogue: O_t / l -> bf16 -> global; each half writes D/2 of the row's columns.
       if (!mbar_wait(&bars->o_final[t], wseq & 1)) {
         report_timeout(p.status, 10 + t);
@@ -608,7 +595,6 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
       }
       ++wseq;
       tc_fence_after();
-      LF_TRACE_EV(31);
       const float inv = 1.f / l_run;
       const int row0 = (g.iq0 + t) * kTileQ + quarter * 32;  // first global row of the warp
       uint32_t orr[D / 64][32];
@@ -619,7 +605,6 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->o_free[t]);
-      LF_TRACE_EV(32);
       // The warp's 32 rows x 32 columns go to its staging buffer in the 64-byte swizzle of the
       // output tensor map (16-byte piece q of row r at position q ^ ((r >> 1) & 3), conflict
       // free), and one bulk tensor store moves them to global memory; rows past Sq are clipped
@@ -651,10 +636,8 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
       // The buffer is written again (by the partner, with its row sum) at the end of the next
       // item; this warp confirms that the store has read it before its first P of that item.
       store_pending = true;
-      LF_TRACE_EV(27);
     }
     if (lane == 0) tma_store_wait_all();  // all output stores of this warp are complete
-    LF_TRACE_END();
   }
 
   // ---------------- teardown ----------------

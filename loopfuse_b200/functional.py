@@ -72,8 +72,69 @@ def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scal
                       window: int = 0, causal_offset: int = 0,
                       out: Optional[torch.Tensor] = None,
                       status: Optional[torch.Tensor] = None,
-                      dbg_ranges: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """softmax(mask(mods(scale * q k^T))) v for q [B,Hq,Sq,D], k/v [B,Hkv,Skv,D] (bf16)."""
+                      dbg_ranges: Optional[torch.Tensor] = None,
+                      kv_tile: int = 0) -> torch.Tensor:
+    """softmax(mask(mods(scale * q k^T))) v for q [B,Hq,Sq,D], k/v [B,Hkv,Skv,D] (bf16).
+
+    ``kv_tile`` pins the KV tile of the kernel (64 or 128 keys; 0 lets the library choose)."""
+    a, out, dev = _prefill_args(q, k, v, scale, mods, mask_kind, window, causal_offset, out,
+                                status, dbg_ranges, kv_tile)
+    with torch.cuda.device(dev):
+        rc = _native.load().lf_prefill_bf16(C.byref(a), _stream_ptr(dev))
+    _native.check(rc, "lf_prefill_bf16")
+    return out
+
+
+class PreparedPrefill:
+    """A prefill call bound once to its tensors and parameters, for loops that launch the same
+    problem again and again (a serving step, a benchmark): the argument record of the C ABI is
+    filled and validated a single time, ``run()`` only launches. This is the per-call host work
+    the reference's generated launcher repeats on every call (loopfuse/codegen.py:215-298:
+    output allocation, stride extraction, grid computation). The tensors are kept alive by the
+    object; new data written into the same buffers is picked up by the next ``run()``."""
+
+    def __init__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float = 1.0,
+                 mods: Sequence[ScoreMod] = (), mask_kind: int = MASK_NONE, window: int = 0,
+                 causal_offset: int = 0, out: Optional[torch.Tensor] = None,
+                 status: Optional[torch.Tensor] = None, kv_tile: int = 0) -> None:
+        self._args, self.out, self._dev = _prefill_args(
+            q, k, v, scale, mods, mask_kind, window, causal_offset, out, status, None, kv_tile)
+        self._keep = (q, k, v, status)
+        self._fn = _native.load().lf_prefill_bf16
+        self._ref = C.byref(self._args)
+        self._dev_index = self._dev.index if self._dev.index is not None else \
+            torch.cuda.current_device()
+
+    def run(self, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Launch on the current stream of the tensors' device (which must be the current
+        device); ``out`` replaces the output buffer (same shape and strides) for this and later
+        runs."""
+        if out is not None:
+            if out.shape != self.out.shape or out.stride() != self.out.stride():
+                raise ValueError("out must match the prepared output's shape and strides")
+            self.out = out
+            self._args.out = out.data_ptr()
+        rc = self._fn(self._ref, torch.cuda.current_stream(self._dev_index).cuda_stream)
+        if rc:
+            _native.check(rc, "lf_prefill_bf16")
+        return self.out
+
+
+def prefill_kv_tile(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float = 1.0,
+                    mods: Sequence[ScoreMod] = (), mask_kind: int = MASK_NONE, window: int = 0,
+                    causal_offset: int = 0, kv_tile: int = 0) -> int:
+    """KV tile size (64 or 128 keys) of the kernel ``prefill_attention`` runs for these
+    arguments; skip ranges and ``dbg_ranges`` are in units of it."""
+    a, _, _ = _prefill_args(q, k, v, scale, mods, mask_kind, window, causal_offset, q,
+                            None, None, kv_tile)
+    rc = _native.load().lf_prefill_kv_tile(C.byref(a))
+    if rc < 0:
+        _native.check(rc, "lf_prefill_kv_tile")
+    return rc
+
+
+def _prefill_args(q, k, v, scale, mods, mask_kind, window, causal_offset, out, status,
+                  dbg_ranges, kv_tile):
     dev = _require_cuda(q, k, v)
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
         _check_bf16_lastdim(t, n)
@@ -106,10 +167,8 @@ def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scal
         if dbg_ranges.dtype != torch.int32 or dbg_ranges.numel() < need or not dbg_ranges.is_cuda:
             raise ValueError(f"dbg_ranges must be a CUDA int32 tensor with >= {need} elements")
         a.dbg_ranges = dbg_ranges.data_ptr()
-    with torch.cuda.device(dev):
-        rc = _native.load().lf_prefill_bf16(C.byref(a), _stream_ptr(dev))
-    _native.check(rc, "lf_prefill_bf16")
-    return out
+    a.kv_tile = int(kv_tile)
+    return a, out, dev
 
 
 class DecodeWorkspace:
@@ -130,7 +189,7 @@ _default_ws = DecodeWorkspace()
 
 
 def _decode_common(q, out, B, Hkv, G, Skv, D, scale, mods, splits, workspace, status, dev,
-                   paged=False):
+                   page_size=0):
     a = _native.LfDecodeArgs()
     a.q, a.out = q.data_ptr(), out.data_ptr()
     a.B, a.Hkv, a.G, a.Skv, a.D = B, Hkv, G, Skv, D
@@ -140,7 +199,7 @@ def _decode_common(q, out, B, Hkv, G, Skv, D, scale, mods, splits, workspace, st
     _fill_mods(a, scale, mods)
     lib = _native.load()
     with torch.cuda.device(dev):
-        n_splits = splits if splits else lib.lf_decode_auto_splits(B, Hkv, G, Skv, D, int(paged))
+        n_splits = splits if splits else lib.lf_decode_auto_splits(B, Hkv, G, Skv, D, page_size)
     a.splits = n_splits
     nbytes = lib.lf_decode_workspace_bytes(B, Hkv, G, D, n_splits)
     ws = (workspace or _default_ws).get(nbytes, dev)
@@ -228,7 +287,7 @@ def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
     if out is None:
         out = torch.empty((B, Hkv, G, D), dtype=torch.bfloat16, device=dev)
     a, ws = _decode_common(q, out, B, Hkv, G, Skv, D, scale, mods, splits, workspace, status, dev,
-                           paged=True)
+                           page_size=page_size)
     a.k, a.v = k_pool.data_ptr(), v_pool.data_ptr()
     for i in range(3):
         a.k_stride[i] = k_pool.stride(i)
@@ -261,3 +320,55 @@ def paged_gather(pool: torch.Tensor, block_table: torch.Tensor, *, seq_len: Opti
             _stream_ptr(dev))
     _native.check(rc, "lf_paged_gather_bf16")
     return out
+
+
+def kv_append(k_new: torch.Tensor, v_new: torch.Tensor, k_pool: torch.Tensor,
+              v_pool: torch.Tensor, block_table: torch.Tensor, *,
+              seq_pos: Optional[torch.Tensor] = None, start_pos: int = 0,
+              block_table_v: Optional[torch.Tensor] = None,
+              status: Optional[torch.Tensor] = None) -> None:
+    """Write new K/V rows ``[B, Hkv, T, D]`` into the pages of a paged cache, in place: token i
+    of sequence b goes to ``pool[block_table[b, pos // page_size], pos % page_size]`` with
+    ``pos = seq_pos[b] + i`` (or ``start_pos + i``). The device-side producer of the cache that
+    ``paged_decode_attention`` reads."""
+    dev = _require_cuda(k_new, v_new, k_pool, v_pool, block_table)
+    for t_, n_ in ((k_new, "k_new"), (v_new, "v_new")):
+        _check_bf16_lastdim(t_, n_)
+        if t_.dim() != 4:
+            raise ValueError(f"{n_} must be [B, Hkv, T, D]")
+    kp = _pool_view(k_pool, "k_pool")
+    vp = _pool_view(v_pool, "v_pool")
+    B, Hkv, T, D = k_new.shape
+    if v_new.shape != k_new.shape:
+        raise ValueError("k_new and v_new must have the same shape")
+    if kp.shape[2] != Hkv or kp.shape[3] != D or vp.shape != kp.shape:
+        raise ValueError(f"pool shape mismatch: new {tuple(k_new.shape)} pool {tuple(kp.shape)}")
+    bt = _table_i32(block_table)
+    btv = _table_i32(block_table_v) if block_table_v is not None else None
+    if bt.shape[0] != B:
+        raise ValueError("block_table batch mismatch")
+    if btv is not None and (btv.shape != bt.shape or btv.stride(0) != bt.stride(0)):
+        btv, bt = btv.contiguous(), bt.contiguous()
+    if seq_pos is not None:
+        if seq_pos.dtype != torch.int32 or seq_pos.shape != (B,) or not seq_pos.is_cuda:
+            raise ValueError("seq_pos must be a CUDA int32 tensor of shape [B]")
+        seq_pos = seq_pos.contiguous()
+    a = _native.LfKvAppendArgs()
+    a.k_new, a.v_new = k_new.data_ptr(), v_new.data_ptr()
+    a.k_pool, a.v_pool = kp.data_ptr(), vp.data_ptr()
+    a.block_table = bt.data_ptr()
+    a.block_table_v = btv.data_ptr() if btv is not None else None
+    a.seq_pos = seq_pos.data_ptr() if seq_pos is not None else None
+    a.start_pos = int(start_pos)
+    a.B, a.Hkv, a.T, a.D = B, Hkv, T, D
+    for i in range(3):
+        a.kn_stride[i] = k_new.stride(i)
+        a.vn_stride[i] = v_new.stride(i)
+        a.kp_stride[i] = kp.stride(i)
+        a.vp_stride[i] = vp.stride(i)
+    a.bt_stride, a.bt_blocks = bt.stride(0), bt.shape[1]
+    a.page_size, a.n_pages = kp.shape[1], kp.shape[0]
+    a.status = status.data_ptr() if status is not None else None
+    with torch.cuda.device(dev):
+        rc = _native.load().lf_kv_append_bf16(C.byref(a), _stream_ptr(dev))
+    _native.check(rc, "lf_kv_append_bf16")

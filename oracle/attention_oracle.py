@@ -16,6 +16,9 @@ What each function follows (paths inside tomatillos/loopfuse):
   paged_load_ref      loopfuse/torch_backend/__init__.py:46-56
   attention_ref       the user-level functions of tests/benchmark.py:79-83, 142-147, 221-230,
                       328-334, 481-484 and tests/test_accuracy.py:131-135
+  kv_append_ref       the inverse of paged_load_ref: the cache / table convention of
+                      tests/benchmark.py:308-319 read by loopfuse/torch_backend/__init__.py:46-56,
+                      used as an indexed store (pool[block_table[b, t // P], t % P] = new row)
   reference_skip_range     closed forms of the range rewrite in
                       loopfuse/compiler/passes/skip_loop_iterations.py:343-376
   brute_force_skip_range   definition of a live tile ("holds >= 1 unmasked in-bounds element")
@@ -84,6 +87,27 @@ def physical_rows(block_table: torch.Tensor, page_size: int, seq_len: int) -> to
 # ---------------------------------------------------------------------------------------------
 # attention
 # ---------------------------------------------------------------------------------------------
+def kv_append_ref(k_pool: torch.Tensor, new: torch.Tensor, block_table: torch.Tensor,
+                  seq_pos) -> torch.Tensor:
+    """Append ``new`` [B, Hkv, T, D] to a paged pool [n_pages, P, Hkv, D] (or [n_pages, Hkv, D],
+    P = 1): returns a copy of the pool with pool[table[b, t // P], t % P, h] = new[b, h, t - pos_b]
+    for t in [pos_b, pos_b + T). ``seq_pos`` is an int (all sequences) or a per-sequence list.
+    A plain Python loop over (sequence, token): the definition, not a fast path."""
+    pool = k_pool.clone()
+    squeeze = pool.dim() == 3
+    if squeeze:
+        pool = pool.unsqueeze(1)
+    P = pool.shape[1]
+    B, Hkv, T, D = new.shape
+    for b in range(B):
+        pos0 = int(seq_pos if isinstance(seq_pos, int) else seq_pos[b])
+        for i in range(T):
+            t = pos0 + i
+            page = int(block_table[b, t // P])
+            pool[page, t % P] = new[b, :, i]
+    return pool.squeeze(1) if squeeze else pool
+
+
 def apply_mods(s: torch.Tensor, mods: Sequence[tuple]) -> torch.Tensor:
     """Score-mod chain as (name, arg) pairs, e.g. [("div", 50.0), ("tanh", None), ("mul", 50.0)]."""
     for name, arg in mods:

@@ -72,3 +72,23 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
         assert "no fallback" in str(e)
     else:
         raise AssertionError("load() must raise when the library is missing")
+
+
+def test_build_fingerprint_covers_every_included_file():
+    """Every file a .cu under csrc/ #includes from the source tree is part of the rebuild
+    fingerprint, so editing any of them rebuilds the library."""
+    import re
+    from loopfuse_b200 import build as B
+    covered = {p.resolve() for p in B.fingerprint_files()}
+    seen, todo = set(), [p for p in B.CSRC.glob("*.cu")]
+    while todo:
+        f = todo.pop()
+        if f in seen:
+            continue
+        seen.add(f)
+        for inc in re.findall(r'#include\s+"([^"]+)"', f.read_text()):
+            target = (f.parent / inc).resolve()
+            assert target.exists(), f"{f.name} includes missing {inc}"
+            assert target in covered, f"{target} is not in the build fingerprint"
+            todo.append(target)
+    assert any(p.name == "lf_prefill_wide.cuh" for p in seen)

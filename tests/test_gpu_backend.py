@@ -66,21 +66,62 @@ def test_reference_style_gqa_test_shape():
 
 
 def test_reference_style_paged_prefill():
-    # tests/test_accuracy.py:253-278: paged K (one token per page) with a causal prefill
+    # tests/test_accuracy.py:253-278: K through paged_load (one token per page, random table
+    # with repeats), V dense, causal prefill
     def fn(Q, K_cache, K_block_table, V):
         K = torch.ops.loopfuse.paged_load(K_cache, K_block_table).transpose(1, 2)
         QK = Q @ K.transpose(-2, -1) * (Q.shape[-1] ** -0.5)
         return torch.softmax(torch.ops.loopfuse.causal_mask(QK), dim=-1) @ V
 
     g = torch.Generator().manual_seed(6)
-    B, H, S_, D = 2, 4, 384, 64
+    B, H, S_, D = 4, 8, 1024, 64
     Kc = torch.randn(B * S_ * 2, H, D, generator=g).bfloat16()
     bt = torch.randint(0, B * S_ * 2, (B, S_), generator=g, dtype=torch.int32)
     Q = torch.randn(B, H, S_, D, generator=g).bfloat16()
     V = torch.randn(B, H, S_, D, generator=g).bfloat16()
-    with pytest.raises(Exception):
-        # K paged but V dense is outside what the binder supports; it must raise, not fall back
-        compile_and_run(fn, (Q, Kc, bt, V))
+    out = compile_and_run(fn, (Q, Kc, bt, V))
+    K = O.paged_load_ref(Kc, bt.long()).transpose(1, 2)          # [B, H, S, D]
+    want = O.attention_ref(Q, K, V, mask="causal", batch_chunk=B)
+    assert (out.float().cpu() - want).abs().max().item() <= TOL
+
+
+def test_reference_style_paged_prefill_gqa():
+    # tests/test_accuracy.py:281-311: the same with grouped heads (repeat_interleave of the
+    # paged K and of the dense V)
+    def fn(Q, K_cache, K_block_table, V):
+        K = torch.ops.loopfuse.paged_load(K_cache, K_block_table).transpose(1, 2)
+        Hq_, Hk_ = Q.shape[1], K.shape[1]
+        K = K.repeat_interleave(Hq_ // Hk_, dim=1)
+        V = V.repeat_interleave(Hq_ // Hk_, dim=1)
+        QK = Q @ K.transpose(-2, -1) * (Q.shape[-1] ** -0.5)
+        return torch.softmax(torch.ops.loopfuse.causal_mask(QK), dim=-1) @ V
+
+    g = torch.Generator().manual_seed(7)
+    B, Hq, Hk, S_, D = 4, 8, 4, 256, 64
+    Kc = torch.randn(B * S_ * 2, Hk, D, generator=g).bfloat16()
+    bt = torch.randint(0, B * S_ * 2, (B, S_), generator=g, dtype=torch.int32)
+    Q = torch.randn(B, Hq, S_, D, generator=g).bfloat16()
+    V = torch.randn(B, Hk, S_, D, generator=g).bfloat16()
+    out = compile_and_run(fn, (Q, Kc, bt, V))
+    K = O.paged_load_ref(Kc, bt.long()).transpose(1, 2)
+    want = O.attention_ref(Q, K, V, mask="causal", batch_chunk=B)
+    assert (out.float().cpu() - want).abs().max().item() <= TOL
+
+
+def test_status_word_is_checked_when_asked(monkeypatch):
+    """LF_CHECK_STATUS=1: an out-of-range block-table entry raises through the compiled
+    function (the reference's eager gather would raise an index error); the kernel itself
+    clamps the address, nothing faults."""
+    monkeypatch.setenv("LF_CHECK_STATUS", "1")
+    w = dataclasses.replace(WORKLOADS["paged_decode_gqa"], B=2, S=512, pages_per_seq=32)
+    q, kp, vp, table = make_inputs(w)
+    bad = table.clone()
+    bad[1, 3] = kp.shape[0] + 7
+    with pytest.raises(Exception, match="page id"):
+        compile_and_run(w.fn(), (q, kp, vp, bad))
+    out = compile_and_run(w.fn(), (q, kp, vp, table))         # the next call is clean again
+    want = O.workload_ref(w, (q, kp, vp, table))
+    assert (out.float().cpu() - want).abs().max().item() <= TOL
 
 
 def test_cpu_tensors_fail_loudly():

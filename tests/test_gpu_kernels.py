@@ -227,20 +227,26 @@ def test_prefill_config1_full():
     assert max_err(out, O.workload_ref(w, (q, k, v), batch_chunk=2)) <= TOL
 
 
-@pytest.mark.parametrize("S_,scale_in", [(512, 1.0), (593, 3.0)])
-def test_prefill_softcap(S_, scale_in):
+KV_TILES = [64, 128]   # the two bounded-softcap kernels (64-key and 128-key KV tiles)
+
+
+@pytest.mark.parametrize("kv_tile", KV_TILES)
+@pytest.mark.parametrize("S_,scale_in", [(512, 1.0), (593, 3.0), (100, 1.0), (2048, 6.0)])
+def test_prefill_softcap(S_, scale_in, kv_tile):
     q, k, v = _prefill_case(1, 4, 4, S_, S_, 128, scale=scale_in)
-    out = _run_prefill(q, k, v, scale=128 ** -0.5, mods=SOFTCAP, mask_kind=S.MASK_CAUSAL)
+    out = _run_prefill(q, k, v, scale=128 ** -0.5, mods=SOFTCAP, mask_kind=S.MASK_CAUSAL,
+                       kv_tile=kv_tile)
     want = O.attention_ref(q, k, v, mods=O.softcap_mods(50.0), mask="causal")
     assert max_err(out, want) <= TOL
 
 
+@pytest.mark.parametrize("kv_tile", KV_TILES)
 @pytest.mark.parametrize("S_,W,G", [(1024, 256, 4), (593, 130, 2), (640, 258, 1), (300, 1024, 4),
-                                    (512, 1, 1), (2048, 256, 4)])
-def test_prefill_window_gqa_softcap(S_, W, G):
+                                    (512, 1, 1), (2048, 256, 4), (900, 64, 2)])
+def test_prefill_window_gqa_softcap(S_, W, G, kv_tile):
     q, k, v = _prefill_case(1, 2 * G, 2, S_, S_, 128, scale=2.0)
     out = _run_prefill(q, k, v, scale=128 ** -0.5, mods=SOFTCAP,
-                       mask_kind=S.MASK_CAUSAL_WINDOW, window=W)
+                       mask_kind=S.MASK_CAUSAL_WINDOW, window=W, kv_tile=kv_tile)
     want = O.attention_ref(q, k, v, mods=O.softcap_mods(50.0), mask="window", window=W)
     assert max_err(out, want) <= TOL
 
@@ -295,27 +301,36 @@ def test_kernel_iterates_exactly_the_analysed_skip_ranges(kind, W, S_):
                                                      keep=keep)
 
 
+@pytest.mark.parametrize("kv_tile", KV_TILES)
 @pytest.mark.parametrize("kind,W,S_", [(S.MASK_CAUSAL, 0, 2048), (S.MASK_CAUSAL_WINDOW, 256, 2048),
                                        (S.MASK_CAUSAL_WINDOW, 130, 593), (S.MASK_NONE, 0, 400)])
-def test_persistent_softcap_kernel_iterates_exactly_the_analysed_skip_ranges(kind, W, S_):
-    """The same bit-exact check for the persistent kernel that softcap(50) selects (more work
-    items than SMs, so every CTA walks several items)."""
+def test_persistent_softcap_kernel_iterates_exactly_the_analysed_skip_ranges(kind, W, S_, kv_tile):
+    """The same bit-exact check for the persistent kernels that softcap(50) selects (more work
+    items than SMs, so every CTA walks several items), in units of the kernel's own KV tile."""
     B, H, D = 3, 32, 64
     q, k, v = _prefill_case(B, H, 8, S_, S_, D)
     n_qt = -(-S_ // S.TILE_Q)
     dbg = torch.full((B * H * n_qt * 2,), -1, dtype=torch.int32, device=DEV)
-    _run_prefill(q, k, v, scale=0.125, mods=SOFTCAP, mask_kind=kind, window=W, dbg_ranges=dbg)
+    kw = dict(scale=0.125, mods=SOFTCAP, mask_kind=kind, window=W, kv_tile=kv_tile)
+    assert F.prefill_kv_tile(q.to(DEV), k.to(DEV), v.to(DEV), **kw) == kv_tile
+    _run_prefill(q, k, v, dbg_ranges=dbg, **kw)
     got = dbg.view(B * H, n_qt, 2).cpu()
-    table = S.skip_table(kind, W, 0, S_, S_)
+    table = S.skip_table(kind, W, 0, S_, S_, tile_k=kv_tile)
+    mask = {S.MASK_NONE: "none", S.MASK_CAUSAL: "causal", S.MASK_CAUSAL_WINDOW: "window"}[kind]
+    keep = O.keep_matrix(mask, W, S_, S_)
     for iq in range(n_qt):
         assert all(tuple(got[u, iq].tolist()) == table[iq] for u in range(B * H))
+        assert table[iq] == O.brute_force_skip_range(mask, W, S_, S_, S.TILE_Q, kv_tile, iq,
+                                                     keep=keep)
 
 
+@pytest.mark.parametrize("kv_tile", KV_TILES)
 @pytest.mark.parametrize("S_,W", [(593, 0), (1024, 200), (130, 64)])
-def test_prefill_softcap_head_dim_64(S_, W):
+def test_prefill_softcap_head_dim_64(S_, W, kv_tile):
     q, k, v = _prefill_case(2, 4, 2, S_, S_, 64, scale=1.5)
     kind = S.MASK_CAUSAL_WINDOW if W else S.MASK_CAUSAL
-    out = _run_prefill(q, k, v, scale=64 ** -0.5, mods=SOFTCAP, mask_kind=kind, window=W)
+    out = _run_prefill(q, k, v, scale=64 ** -0.5, mods=SOFTCAP, mask_kind=kind, window=W,
+                       kv_tile=kv_tile)
     want = O.attention_ref(q, k, v, mods=O.softcap_mods(50.0), mask="window" if W else "causal",
                            window=W, batch_chunk=2)
     assert max_err(out, want) <= TOL
@@ -331,20 +346,43 @@ def test_prefill_softcap_large_cap_uses_running_max():
     assert max_err(out, want) <= TOL
 
 
-@pytest.mark.parametrize("softcap", [False, True])
+@pytest.mark.parametrize("softcap", [0, 64, 128])   # 0: running-max kernel; else the KV tile
 def test_prefill_rows_without_visible_keys_are_nan(softcap):
     """Diagonal shifted up by 200: query rows 0..199 see no key at all (NaN in the eager
     computation), row 200 sees key 0 only; the first 128-row tile has no KV block to visit."""
     q, k, v = _prefill_case(1, 2, 2, 384, 256, 128)
     mods = SOFTCAP if softcap else []
     out = _run_prefill(q, k, v, scale=128 ** -0.5, mods=mods, mask_kind=S.MASK_CAUSAL,
-                       causal_offset=-200).float().cpu()
+                       causal_offset=-200, kv_tile=softcap).float().cpu()
     want = O.attention_ref(q, k, v, mods=O.softcap_mods(50.0) if softcap else (),
                            mask="causal", offset=-200)
     assert torch.isnan(want[:, :, :200]).all() and not torch.isnan(want[:, :, 200:]).any()
     assert torch.isnan(out[:, :, :200]).all()
     assert (out[:, :, 200:] - want[:, :, 200:]).abs().max().item() <= TOL
     assert torch.equal(out[:, :, 200], v[:, :, 0].float())
+
+
+@pytest.mark.parametrize("kv_tile", KV_TILES)
+@pytest.mark.parametrize("S_,W", [(128, 0), (256, 0), (700, 64)])
+def test_persistent_kernels_many_short_items(S_, W, kv_tile):
+    """Work items of one or two KV blocks, many more of them than SMs: the hand-over between
+    items (row-sum exchange through the output staging buffers, O hand-back, Q prefetch) runs
+    back to back. Repeated launches must agree bit for bit with each other and with the oracle
+    within the tolerance."""
+    B, Hq, Hkv, D = 6, 64, 16, 128
+    q, k, v = _prefill_case(B, Hq, Hkv, S_, S_, D)
+    kind = S.MASK_CAUSAL_WINDOW if W else S.MASK_CAUSAL
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    st = F.new_status(DEV)
+    kw = dict(scale=D ** -0.5, mods=SOFTCAP, mask_kind=kind, window=W, kv_tile=kv_tile, status=st)
+    first = F.prefill_attention(qd, kd, vd, **kw).clone()
+    for _ in range(20):
+        again = F.prefill_attention(qd, kd, vd, **kw)
+        assert torch.equal(again, first)
+    F.check_status(st)
+    want = O.attention_ref(q[:2], k[:2], v[:2], mods=O.softcap_mods(50.0),
+                           mask="window" if W else "causal", window=W, batch_chunk=1)
+    assert max_err(first[:2], want) <= TOL
 
 
 def test_persistent_kernel_launches_on_two_streams():
@@ -363,28 +401,39 @@ def test_persistent_kernel_launches_on_two_streams():
         assert torch.equal(o, ref)
 
 
-def test_prefill_config2_full_size_sample():
-    """cfg 2 at full size on the GPU; the oracle checks batch elements 0 and 7 (it needs ~10 s
-    per element on the CPU)."""
+@pytest.mark.parametrize("kv_tile", KV_TILES)
+def test_prefill_config2_full_size_sample(kv_tile):
+    """cfg 2 at full size on the GPU (the launch the benchmark times). The oracle checks one
+    head of every batch element (a different head each) plus the last head of the last element,
+    so every region of the work queue is covered; it needs about a second per head on the CPU."""
     w = WORKLOADS["causal_softcap"]
     q, k, v = make_inputs(w)
-    out = _run_prefill(q, k, v, scale=w.D ** -0.5, mods=SOFTCAP, mask_kind=S.MASK_CAUSAL)
-    for b in (0, 7):
-        want = O.attention_ref(q[b:b + 1, :8], k[b:b + 1, :8], v[b:b + 1, :8],
+    out = _run_prefill(q, k, v, scale=w.D ** -0.5, mods=SOFTCAP, mask_kind=S.MASK_CAUSAL,
+                       kv_tile=kv_tile)
+    heads = [(b, (5 * b + 3) % w.Hq) for b in range(w.B)] + [(w.B - 1, w.Hq - 1), (0, 0)]
+    for b, h in heads:
+        want = O.attention_ref(q[b:b + 1, h:h + 1], k[b:b + 1, h:h + 1], v[b:b + 1, h:h + 1],
                                mods=O.softcap_mods(50.0), mask="causal")
-        assert max_err(out[b:b + 1, :8], want) <= TOL
+        assert max_err(out[b:b + 1, h:h + 1], want) <= TOL
     # size-independent property: row 0 attends to key 0 only, so out[..., 0, :] == v[..., 0, :]
     assert torch.equal(out[:, :, 0, :].cpu(), v[:, :, 0, :])
 
 
-def test_prefill_config3_full_size_sample():
+@pytest.mark.parametrize("kv_tile", KV_TILES)
+def test_prefill_config3_full_size_sample(kv_tile):
+    """cfg 3 at full size: one kv head (its four query heads) of every batch element, plus the
+    last kv head of the last element."""
     w = WORKLOADS["window_gqa_softcap"]
     q, k, v = make_inputs(w)
     out = _run_prefill(q, k, v, scale=w.D ** -0.5, mods=SOFTCAP,
-                       mask_kind=S.MASK_CAUSAL_WINDOW, window=w.window)
-    want = O.attention_ref(q[3:4], k[3:4], v[3:4], mods=O.softcap_mods(50.0), mask="window",
-                           window=w.window)
-    assert max_err(out[3:4], want) <= TOL
+                       mask_kind=S.MASK_CAUSAL_WINDOW, window=w.window, kv_tile=kv_tile)
+    g = w.group
+    units = [(b, (3 * b + 1) % w.Hkv) for b in range(w.B)] + [(w.B - 1, w.Hkv - 1)]
+    for b, hk in units:
+        qs = slice(hk * g, (hk + 1) * g)
+        want = O.attention_ref(q[b:b + 1, qs], k[b:b + 1, hk:hk + 1], v[b:b + 1, hk:hk + 1],
+                               mods=O.softcap_mods(50.0), mask="window", window=w.window)
+        assert max_err(out[b:b + 1, qs], want) <= TOL
     kv_rep = v[:, :, 0, :].repeat_interleave(w.group, dim=1)
     assert torch.equal(out[:, :, 0, :].cpu(), kv_rep)
 

@@ -121,3 +121,22 @@ def test_generated_bounds_vs_brute_force(skip_golden):
                 mismatches[tab["mask"]] += 1
     assert set(mismatches) <= {"window130"}
     assert mismatches.get("window130", 0) > 0
+
+
+def test_kv_append_is_the_inverse_of_paged_load():
+    """Appending rows through a permutation table and gathering them back with the reference's
+    paged_load semantics returns the rows (the round trip that pins the page-index rule of the
+    cache producer)."""
+    g = torch.Generator().manual_seed(5)
+    n_pages, P, Hkv, D, B, S = 24, 4, 2, 8, 3, 20
+    pool = torch.zeros(n_pages, P, Hkv, D)
+    table = torch.randperm(n_pages, generator=g)[:B * 6].view(B, 6).int()
+    new = torch.randn(B, Hkv, S, D, generator=g)
+    pool = O.kv_append_ref(pool, new[:, :, :13], table, 0)
+    pool = O.kv_append_ref(pool, new[:, :, 13:], table, [13] * B)
+    gathered = O.paged_load_ref(pool, table.long())           # [B, 6, P, Hkv, D]
+    back = gathered.reshape(B, 6 * P, Hkv, D)[:, :S].transpose(1, 2)
+    assert torch.equal(back, new)
+    rows = O.physical_rows(table, P, S)                        # pool row of every (b, t)
+    flat = pool.reshape(n_pages * P, Hkv, D)
+    assert torch.equal(flat[rows.long()].transpose(1, 2), new)
