@@ -198,7 +198,9 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
 
   if (warp == kProducerWarp) {
     // ---------------- TMA producer (and item dispatcher) ----------------
-    if (lane == 0) {
+    // The whole warp runs the loop; the elected lane issues the copies and publishes items.
+    {
+      const bool elected = elect_one_sync();
       int n = 0;                // ring position, runs across items
       int qseq[2] = {0, 0};     // items with work so far, per tile
       bool ok = true;
@@ -212,21 +214,26 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
           ok = false;
           return;
         }
-        mbar_arrive_expect_tx(&bars->kv_full[stage], jb >= 0 ? 2 * kKVTileBytes : kKVTileBytes);
-        unsigned char* dst = sKV + stage * (2 * kKVTileBytes);
-#pragma unroll
-        for (int kb = 0; kb < kBlocksD; ++kb)
-          tma_load_4d(dst + kb * kKVBlockBytes, tma, &bars->kv_full[stage], kb * 64, ja * kTileK,
-                      hkv, b);
-        if (jb >= 0) {
+        if (elected) {
+          mbar_arrive_expect_tx(&bars->kv_full[stage], jb >= 0 ? 2 * kKVTileBytes : kKVTileBytes);
+          unsigned char* dst = sKV + stage * (2 * kKVTileBytes);
 #pragma unroll
           for (int kb = 0; kb < kBlocksD; ++kb)
-            tma_load_4d(dst + kKVTileBytes + kb * kKVBlockBytes, &tmap_k, &bars->kv_full[stage],
-                        kb * 64, jb * kTileK, hkv, b);
+            tma_load_4d(dst + kb * kKVBlockBytes, tma, &bars->kv_full[stage], kb * 64,
+                        ja * kTileK, hkv, b);
+          if (jb >= 0) {
+#pragma unroll
+            for (int kb = 0; kb < kBlocksD; ++kb)
+              tma_load_4d(dst + kKVTileBytes + kb * kKVBlockBytes, &tmap_k, &bars->kv_full[stage],
+                          kb * 64, jb * kTileK, hkv, b);
+          }
         }
+        __syncwarp();
       };
       for (int seq = 0; ok; ++seq) {
-        int it = static_cast<int>(atomicAdd(p.ticket, 1u));
+        int it = 0;
+        if (lane == 0) it = static_cast<int>(atomicAdd(p.ticket, 1u));
+        it = __shfl_sync(0xffffffffu, it, 0);
         if (it >= p.n_items) it = -1;
         const int slot = seq % kItemSlots;
         if (!mbar_wait(&bars->item_empty[slot], ((seq / kItemSlots) & 1) ^ 1)) {
@@ -236,8 +243,11 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
         ItemGeom g;
         if (it >= 0) g = decode_item(p, it);
         else g.it = -1, g.b = g.h = g.hkv = g.iq0 = g.lo0 = g.hi0 = g.lo1 = g.hi1 = g.flags = g.lo = g.hi = 0;
-        item_slots[slot] = g;
-        mbar_arrive(&bars->item_full[slot]);  // release: the slot is visible to the waiters
+        if (elected) {
+          item_slots[slot] = g;
+          mbar_arrive(&bars->item_full[slot]);  // release: the slot is visible to the waiters
+        }
+        __syncwarp();
         if (it < 0) break;
         for (int t = 0; t < 2 && ok; ++t) {
           if (!g.work(t)) continue;
@@ -248,11 +258,14 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
             break;
           }
           ++qseq[t];
-          mbar_arrive_expect_tx(&bars->q_full[t], kQTileBytes);
+          if (elected) {
+            mbar_arrive_expect_tx(&bars->q_full[t], kQTileBytes);
 #pragma unroll
-          for (int kb = 0; kb < kBlocksD; ++kb)
-            tma_load_4d(sQ + t * kQTileBytes + kb * kQBlockBytes, &tmap_q, &bars->q_full[t],
-                        kb * 64, (g.iq0 + t) * kTileQ, g.h, g.b);
+            for (int kb = 0; kb < kBlocksD; ++kb)
+              tma_load_4d(sQ + t * kQTileBytes + kb * kQBlockBytes, &tmap_q, &bars->q_full[t],
+                          kb * 64, (g.iq0 + t) * kTileQ, g.h, g.b);
+          }
+          __syncwarp();
         }
         if (g.hi > g.lo) {
           load_pair(&tmap_k, g.lo, g.lo + 1 < g.hi ? g.lo + 1 : -1, g.hkv, g.b);
@@ -266,9 +279,13 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
     // All four threads walk every ring stage and each releases it (kv_empty counts four
     // arrivals) once the MMAs it issued from the stage, if any, are complete. A thread must see
     // a stage full before it releases it: that keeps its arrivals one per phase.
-    if (lane == 0) {
+    // The whole warp runs the loop (every lane waits on the barriers); the elected lane alone
+    // issues MMAs and commits. A warp that has diverged into a single-lane branch gets far fewer
+    // issue slots next to the busy softmax warps (measured: one MMA per ~150 clocks, not 64).
+    {
       const int t = (warp - kMmaWarp0) & 1;
       const bool is_qk = warp - kMmaWarp0 >= 2;
+      const bool elected = elect_one_sync();
       bool ok = true;
       constexpr uint32_t kStageUnits = (2 * kKVTileBytes) >> 4;  // a stage is a pair of tiles
       constexpr uint32_t kHalfUnits = kKVTileBytes >> 4;
@@ -292,7 +309,7 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
         return stage;
       };
       for (int seq = 0; ok; ++seq) {
-        const ItemGeom g = next_item(seq, false);
+        const ItemGeom g = next_item(seq, true);
         if (g.it < 0) break;
         if (g.hi <= g.lo) continue;
         const int lo = g.lo, hi = g.hi, lo_tt = g.lo_t(t), hi_tt = g.hi_t(t);
@@ -321,15 +338,18 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
             const uint64_t kd =
                 kdesc0 + static_cast<uint64_t>(stage * kStageUnits + hf * kHalfUnits);
             const uint32_t d = s_col + buf * 64;
+            if (elected) {
 #pragma unroll
-            for (int ks = 0; ks < D / 16; ++ks) {
-              mma_ss(d,
-                     qdesc + static_cast<uint64_t>((ks / 4) * (kQBlockBytes >> 4) + (ks % 4) * 2),
-                     kd + static_cast<uint64_t>((ks / 4) * (kKVBlockBytes >> 4) + (ks % 4) * 2),
-                     kIdescQK, ks > 0 ? 1u : 0u);
+              for (int ks = 0; ks < D / 16; ++ks) {
+                mma_ss(d,
+                       qdesc + static_cast<uint64_t>((ks / 4) * (kQBlockBytes >> 4) + (ks % 4) * 2),
+                       kd + static_cast<uint64_t>((ks / 4) * (kKVBlockBytes >> 4) + (ks % 4) * 2),
+                       kIdescQK, ks > 0 ? 1u : 0u);
+              }
+              tc_commit(&bars->s_full[t][buf]);
+              if (j == hi_tt - 1) tc_commit(&bars->q_free[t]);  // Q_t may be overwritten now
             }
-            tc_commit(&bars->s_full[t][buf]);
-            if (j == hi_tt - 1) tc_commit(&bars->q_free[t]);  // Q_t may be overwritten now
+            __syncwarp();
             return true;
           };
           // First stage of the item: {K(lo), K(lo+1)}.
@@ -339,7 +359,8 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
             tc_fence_after();
             if (active(lo) && !issue_qk(stage, 0, lo)) break;
             if (lo + 1 < hi && active(lo + 1) && !issue_qk(stage, 1, lo + 1)) break;
-            tc_commit(&bars->kv_empty[stage]);
+            if (elected) tc_commit(&bars->kv_empty[stage]);
+            __syncwarp();
           }
           for (int j = lo; j < hi && ok; ++j) {
             const int st = wait_stage(4);  // {V(j), K(j+2)}
@@ -348,13 +369,15 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
               tc_fence_after();
               if (!issue_qk(st, 1, j + 2)) break;
             }
-            tc_commit(&bars->kv_empty[st]);
+            if (elected) tc_commit(&bars->kv_empty[st]);
+            __syncwarp();
           }
         } else {
           {  // the first stage of an item holds K tiles only
             const int st = wait_stage(5);
             if (st < 0) break;
-            tc_commit(&bars->kv_empty[st]);
+            if (elected) tc_commit(&bars->kv_empty[st]);
+            __syncwarp();
           }
           for (int j = lo; j < hi && ok; ++j) {
             const int st = wait_stage(5);  // {V(j), K(j+2)}
@@ -376,17 +399,20 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
               tc_fence_after();
               const uint64_t vd = vdesc0 + static_cast<uint64_t>(st * kStageUnits);
               const uint32_t a = s_col + (gj & 1) * 64;
+              if (elected) {
 #pragma unroll
-              for (int ks = 0; ks < kTileK / 16; ++ks) {
-                // P columns of 16 keys: 16 columns at the start of each 32-column half of S.
-                mma_ts(o_col, a + (ks >> 1) * 32 + (ks & 1) * 8,
-                       vd + static_cast<uint64_t>(ks * (2048 >> 4)), kIdescPV,
-                       (kt > 0 || ks > 0) ? 1u : 0u);
+                for (int ks = 0; ks < kTileK / 16; ++ks) {
+                  // P columns of 16 keys: 16 columns at the start of each 32-column half of S.
+                  mma_ts(o_col, a + (ks >> 1) * 32 + (ks & 1) * 8,
+                         vd + static_cast<uint64_t>(ks * (2048 >> 4)), kIdescPV,
+                         (kt > 0 || ks > 0) ? 1u : 0u);
+                }
+                tc_commit(&bars->pv_each[t][gj & 1]);
+                if (j == hi_tt - 1) tc_commit(&bars->o_final[t]);
               }
-              tc_commit(&bars->pv_each[t][gj & 1]);
-              if (j == hi_tt - 1) tc_commit(&bars->o_final[t]);
             }
-            tc_commit(&bars->kv_empty[st]);
+            if (elected) tc_commit(&bars->kv_empty[st]);
+            __syncwarp();
           }
           if (work) ++wseq;
         }
@@ -416,8 +442,6 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
     // the output factor c2 are folded into the coefficients p.qc[] on the host, so the polynomial
     // runs on raw^2 and gives logit2 = raw * q(raw^2) directly; p.ylim[] are the limits of the two
     // polynomials as bounds on raw^2.
-    const uint64_t q0c = pack2(p.qc[0], p.qc[0]);
-    const uint64_t q1c = pack2(p.qc[1], p.qc[1]);
     // The tanh evaluation (0: degree 3, 1: degree 7, 2: MUFU) is chosen speculatively: a block
     // starts with what the warp's previous block needed, and is redone on the spot with a
     // stronger one if its own max |x| (known after the pass) asks for it.
@@ -490,47 +514,39 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
           tmem_wait_ld();
           float psum[4] = {0.f, 0.f, 0.f, 0.f};
           float ymax0 = 0.f, ymax1 = 0.f;
-          auto finish_pair = [&](uint64_t z2, int i, bool apply_mask) {
-            float z0, z1;
-            unpack2(z2, z0, z1);
-            if (apply_mask) {
-              if (i < rel_lo || i > rel_hi) z0 = -INFINITY;
-              if (i + 1 < rel_lo || i + 1 > rel_hi) z1 = -INFINITY;
-            }
-            // Every exponential goes to MUFU: this loop is bound by instruction dispatch, and two
-            // ex2 cost less of it than an FMA-pipe emulation would.
-            const uint32_t pkv = pack_bf16x2(ex2_approx(z0), ex2_approx(z1));
-            pk[i >> 1] = pkv;
-            // The row sum is taken over the bf16-rounded values that the PV product sees, so that
-            // numerator and denominator carry the same rounding (the largest P of a row is not
-            // exactly 1 as it would be with a running max). The mixed-precision add reads the
-            // bf16 halves directly.
-            if ((i >> 1) & 1) add_bf16x2_to_f32(psum[2], psum[3], pkv);
-            else add_bf16x2_to_f32(psum[0], psum[1], pkv);
-          };
+          // Plain fp32 instructions: this loop is bound by instruction issue (12 per pair), and
+          // the packed f32x2 forms, although fewer, take longer in their pipe (measured 1116
+          // against 763 clocks per 32 x 128 scores of a scheduler).
           auto body = [&](auto path_tag, bool apply_mask) {
             constexpr int kPath = decltype(path_tag)::value;
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-              const uint64_t r2 = pack2u(sr[i], sr[i + 1]);
-              const uint64_t y2 = mul2(r2, r2);
-              float y0, y1;
-              unpack2(y2, y0, y1);
+              const float r0 = __uint_as_float(sr[i]), r1 = __uint_as_float(sr[i + 1]);
+              const float y0 = r0 * r0, y1 = r1 * r1;
               if ((i >> 1) & 1) ymax1 = max3(ymax1, y0, y1); else ymax0 = max3(ymax0, y0, y1);
-              uint64_t z2;
+              float z0, z1;
               if constexpr (kPath == 0) {
-                z2 = mul2(r2, fma2(y2, q1c, q0c));
+                z0 = r0 * fmaf(y0, p.qc[1], p.qc[0]);
+                z1 = r1 * fmaf(y1, p.qc[1], p.qc[0]);
               } else if constexpr (kPath == 1) {
-                uint64_t q2 = fma2(y2, pack2(p.qc[3], p.qc[3]), pack2(p.qc[2], p.qc[2]));
-                q2 = fma2(q2, y2, q1c);
-                q2 = fma2(q2, y2, q0c);
-                z2 = mul2(r2, q2);
+                z0 = r0 * fmaf(fmaf(fmaf(y0, p.qc[3], p.qc[2]), y0, p.qc[1]), y0, p.qc[0]);
+                z1 = r1 * fmaf(fmaf(fmaf(y1, p.qc[3], p.qc[2]), y1, p.qc[1]), y1, p.qc[0]);
               } else {
-                const float t0 = tanh_approx(__uint_as_float(sr[i]) * p.a);
-                const float t1 = tanh_approx(__uint_as_float(sr[i + 1]) * p.a);
-                z2 = mul2(pack2(t0, t1), pack2(p.c2, p.c2));
+                z0 = tanh_approx(r0 * p.a) * p.c2;
+                z1 = tanh_approx(r1 * p.a) * p.c2;
               }
-              finish_pair(z2, i, apply_mask);
+              if (apply_mask) {
+                if (i < rel_lo || i > rel_hi) z0 = -INFINITY;
+                if (i + 1 < rel_lo || i + 1 > rel_hi) z1 = -INFINITY;
+              }
+              // The row sum is taken over the bf16-rounded values that the PV product sees, so
+              // that numerator and denominator carry the same rounding (the largest P of a row
+              // is not exactly 1 as it would be with a running max). The mixed-precision add
+              // reads the bf16 halves directly.
+              const uint32_t pkv = pack_bf16x2(ex2_approx(z0), ex2_approx(z1));
+              pk[i >> 1] = pkv;
+              if ((i >> 1) & 1) add_bf16x2_to_f32(psum[2], psum[3], pkv);
+              else add_bf16x2_to_f32(psum[0], psum[1], pkv);
             }
           };
           if (path == 0) {
