@@ -446,9 +446,7 @@ __device__ __forceinline__ void tmem_ld_fence16(uint32_t (&r)[16]) {
   asm volatile(""
                : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]),
                  "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]),
-                 "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
-               :
-               : "memory");
+                 "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]));
 }
 
 // 32 lanes x 8 consecutive 32-bit columns.
@@ -475,6 +473,35 @@ __device__ __forceinline__ void tmem_st_32x32b_x8(uint32_t taddr, const uint32_t
       : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
         "r"(r[7])
       : "memory");
+}
+
+// ---------------------------------------------------------------------------------------
+// Tensor-memory access without a compiler-level memory barrier.
+//
+// The wrappers above carry a "memory" clobber, which also stops the compiler from moving plain
+// arithmetic across them: a load issued in the middle of a computation then cuts it in two
+// halves that cannot overlap. These forms are only ordered among themselves (volatile) and
+// through their register operands: after tmem_wait_ld_async(), pass the destination registers
+// through tmem_ld_fence16() before the first use.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_ld16_async(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_ld_async() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;");
+}
+__device__ __forceinline__ void tmem_st8_async(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+      :
+      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]));
 }
 
 }  // namespace lf

@@ -888,15 +888,14 @@ static int launch_prefill_wide(const CUtensorMap& mq, const CUtensorMap& mk,
   return check_launch("prefill_wide_kernel");
 }
 
-// KV tile of the kernel that serves these arguments: 128 keys for the bounded-softcap kernel
-// unless the caller pins 64 (or the window is so short that 128-key blocks would be mostly
-// masked), 64 keys for every running-max kernel.
+// KV tile of the kernel that serves these arguments. The bounded-softcap mode has two kernels:
+// 64-key tiles (two S buffers per query tile, the default: the faster of the two on every
+// configuration measured) and 128-key tiles (one S buffer, math-bound N=128 QK^T MMAs), which a
+// caller can pin with kv_tile = 128. Every running-max kernel uses 64-key tiles.
 static int choose_kv_tile(const LfPrefillArgs* a, int mode) {
   if (a->kv_tile != 0 && a->kv_tile != kTileK && a->kv_tile != kWideK) return LF_ERR_INVALID_ARG;
   if (mode != kModeBounded) return a->kv_tile == kWideK ? LF_ERR_UNSUPPORTED : kTileK;
-  if (a->kv_tile != 0) return a->kv_tile;
-  if (a->mask_kind == LF_MASK_CAUSAL_WINDOW && a->window < kWideK) return kTileK;
-  return kWideK;
+  return a->kv_tile != 0 ? a->kv_tile : kTileK;
 }
 
 // `launch` == nullptr: only resolve the kernel choice and return its KV tile size.

@@ -506,16 +506,16 @@ __global__ void __launch_bounds__(kWideThreads, 1)
               if (!again) l_run += (ps[0] + ps[1]) + (ps[2] + ps[3]);
             } while (again);
           }
-          tmem_st_32x32b_x8(s_addr + c * 8, pk);
+          tmem_st8_async(s_addr + c * 8, pk);
         };
         tmem_wait_ld();
         tmem_ld_fence16(sa);
         tmem_ld_fence16(sb);
         piece(sa, 0);
-        tmem_ld_32x32b_x16(s_addr + 32, sa);
+        tmem_ld16_async(s_addr + 32, sa);
         piece(sb, 1);
-        tmem_ld_32x32b_x16(s_addr + 48, sb);
-        tmem_wait_ld();
+        tmem_ld16_async(s_addr + 48, sb);
+        tmem_wait_ld_async();
         tmem_ld_fence16(sa);
         tmem_ld_fence16(sb);
         piece(sa, 2);
