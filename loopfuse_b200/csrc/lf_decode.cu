@@ -314,8 +314,9 @@ __global__ void __launch_bounds__(kDecodeThreads)
 //         wants; output column n of MMA (h, e) stands for d = 64h + 8n + e.
 //   The fp32 score fragment of the QK MMAs has the layout of the bf16 A fragment of the PV
 //   MMA, so P never leaves registers.
-// A CTA is one (batch, kv head, KV split); its 4 warps take alternate 16-token groups (one
-// page when page_size is 16) and are merged through shared memory like above.
+// A CTA is one (batch, kv head, KV split); its WARPS warps (4, or 2 when smaller CTAs let the
+// whole grid be resident at once) take alternate 16-token groups (one page when page_size is
+// 16) and are merged through shared memory like above.
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void mma_16816_rows0to7(float& d0, float& d1, uint32_t a0, uint32_t a2,
                                                    uint32_t b0, uint32_t b1) {
@@ -326,8 +327,8 @@ __device__ __forceinline__ void mma_16816_rows0to7(float& d0, float& d1, uint32_
       : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.f), "f"(0.f));
 }
 
-template <int D, bool PAGED, bool HAS_MOD>
-__global__ void __launch_bounds__(kDecodeThreads, 3)
+template <int D, bool PAGED, bool HAS_MOD, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 12 / WARPS)
     decode_mma_kernel(const DecodeParams p, const int G) {
   constexpr int KI = D / 32;  // 16-byte pieces of a K row per lane
   constexpr int VH = D / 64;  // 64-wide halves of a V row
@@ -364,7 +365,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
       const int32_t* bt = (which == 0 ? p.block_table : p.block_table_v) +
                           static_cast<int64_t>(b) * p.bt_stride + first_page;
       int32_t* dst = which == 0 ? s_pages_k : s_pages_v;
-      for (int i = threadIdx.x; i < n_pages_local; i += kDecodeThreads) {
+      for (int i = threadIdx.x; i < n_pages_local; i += (WARPS * 32)) {
         int32_t pg = bt[i];
         if (pg < 0 || pg >= p.n_pages) {
           if (p.status) atomicExch(p.status, LF_DEV_BAD_PAGE);
@@ -471,11 +472,11 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
   };
   const int tg0 = t0 + warp * 16;
 #pragma unroll
-  for (int st = 0; st < kMmaStages - 1; ++st) copy_group(tg0 + st * 16 * kDecodeWarps, st);
+  for (int st = 0; st < kMmaStages - 1; ++st) copy_group(tg0 + st * 16 * WARPS, st);
 
   int it = 0;
-  for (int tg = tg0; tg < t1; tg += 16 * kDecodeWarps, ++it) {
-    copy_group(tg + (kMmaStages - 1) * 16 * kDecodeWarps, (it + kMmaStages - 1) % kMmaStages);
+  for (int tg = tg0; tg < t1; tg += 16 * WARPS, ++it) {
+    copy_group(tg + (kMmaStages - 1) * 16 * WARPS, (it + kMmaStages - 1) % kMmaStages);
     cp_async_wait<kMmaStages - 1>();
     __syncwarp();
     const unsigned char* stage = ring + (it % kMmaStages) * kStageBytes;
@@ -582,17 +583,17 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
   }
   __syncthreads();
 
-  for (int idx = threadIdx.x; idx < G * D; idx += kDecodeThreads) {
+  for (int idx = threadIdx.x; idx < G * D; idx += (WARPS * 32)) {
     const int gg = idx / D;
     const int cc = idx - gg * D;
     float m_all = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kDecodeWarps; ++w)
+    for (int w = 0; w < WARPS; ++w)
       m_all = fmaxf(m_all, s_merge[(w * G + gg) * kStride + D]);
     const float m_safe = (m_all == -INFINITY) ? 0.f : m_all;
     float l_all = 0.f, acc = 0.f;
 #pragma unroll
-    for (int w = 0; w < kDecodeWarps; ++w) {
+    for (int w = 0; w < WARPS; ++w) {
       const float* src = s_merge + (w * G + gg) * kStride;
       const float a = ex2_approx(src[D] - m_safe);
       l_all += src[D + 1] * a;
@@ -752,22 +753,11 @@ static int choose_splits(int B, int Hkv, int G, int Skv, int D, int page_size) {
   int s;
   if (uses_mma_kernel(G, paged)) {
     // Two CTAs of the tensor-core kernel are resident per SM and each keeps ~16 KB in flight
-    // per warp, so one full wave saturates HBM. Splitting costs the partial round trip and a
-    // shorter loop per CTA, so split only as far as the last wave needs: take the smallest
-    // split count whose CTA count fills at least 95 % of its last wave (512 units on 296 slots
-    // are 1.73 waves unsplit, 6.92 waves split four ways).
+    // per warp, so one wave already saturates HBM: split only to fill the machine (splitting
+    // costs the partial round trip and a short, badly pipelined loop per CTA; splitting four
+    // ways to even out the waves of 512 units measured 20 % slower than not splitting).
     const int resident = sms * 2;
-    s = 1;
-    double best = 0.0;
-    for (int cand = 1; cand <= max_by_len; ++cand) {
-      const double waves = static_cast<double>(units) * cand / resident;
-      const double eff = waves / static_cast<double>(static_cast<int64_t>(waves + 0.999999));
-      if (eff > best + 1e-9) {
-        best = eff;
-        s = cand;
-      }
-      if (eff >= 0.95) break;
-    }
+    s = units >= resident ? 1 : (resident + units - 1) / units;
   } else {
     // The FMA kernel has ~8 small CTAs per SM: aim for >= 6 waves so the tail wave is cheap.
     s = (sms * 8 * 6 + units - 1) / units;
@@ -793,34 +783,50 @@ static int launch_decode_g(const DecodeParams& p, cudaStream_t st, size_t smem) 
   return check_launch("decode_split_kernel");
 }
 
-template <int D, bool PAGED>
-static int launch_decode_mma(const DecodeParams& p, int G, cudaStream_t st, size_t smem) {
+// Warps per CTA of the tensor-core kernel. Four warps (two CTAs resident per SM, K/V rings of
+// 96 KB each at D = 128) by default. When the grid is more than one wave of such CTAs but fits
+// in one wave of half-sized ones (four resident per SM, same bytes in flight per SM), two warps:
+// 512 CTAs on 148 SMs are 1.73 waves of the large shape, whose second wave leaves a quarter of
+// the machine idle, but a single resident grid of the small one.
+static int mma_warps_per_cta(int64_t ctas) {
+  const int sms = device_sm_count();
+  return (ctas > 2ll * sms && ctas <= 4ll * sms) ? 2 : 4;
+}
+
+template <int D, bool PAGED, bool HAS_MOD, int WARPS>
+static int launch_decode_mma_w(const DecodeParams& p, int G, cudaStream_t st, size_t table_bytes) {
   dim3 grid(p.splits, p.Hkv, p.B);
   // page ids + the per-warp K/V rings (the warp-merge area reuses the rings)
-  const size_t ring = static_cast<size_t>(kDecodeWarps) * kMmaStages * 2 * 16 * D * 2;
-  const size_t merge = static_cast<size_t>(kDecodeWarps) * G * (D + 2) * sizeof(float);
-  smem = smem - merge + (ring > merge ? ring : merge);
-  static thread_local int configured_dev[2] = {-1, -1};
+  const size_t ring = static_cast<size_t>(WARPS) * kMmaStages * 2 * 16 * D * 2;
+  const size_t merge = static_cast<size_t>(WARPS) * G * (D + 2) * sizeof(float);
+  const size_t smem = table_bytes + (ring > merge ? ring : merge);
+  static thread_local int configured_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
-  if (configured_dev[p.mods.n > 0] != dev) {
-    cudaError_t e =
-        p.mods.n > 0
-            ? cudaFuncSetAttribute(decode_mma_kernel<D, PAGED, true>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024)
-            : cudaFuncSetAttribute(decode_mma_kernel<D, PAGED, false>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+  if (configured_dev != dev) {
+    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<D, PAGED, HAS_MOD, WARPS>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
     if (e != cudaSuccess) {
       set_cuda_error(e, "cudaFuncSetAttribute(decode_mma_kernel)");
       return LF_ERR_CUDA;
     }
-    configured_dev[p.mods.n > 0] = dev;
+    configured_dev = dev;
   }
-  if (p.mods.n > 0)
-    decode_mma_kernel<D, PAGED, true><<<grid, kDecodeThreads, smem, st>>>(p, G);
-  else
-    decode_mma_kernel<D, PAGED, false><<<grid, kDecodeThreads, smem, st>>>(p, G);
+  decode_mma_kernel<D, PAGED, HAS_MOD, WARPS><<<grid, WARPS * 32, smem, st>>>(p, G);
   return check_launch("decode_mma_kernel");
+}
+
+template <int D, bool PAGED>
+static int launch_decode_mma(const DecodeParams& p, int G, cudaStream_t st, size_t smem) {
+  // `smem` arrives as warp-merge area (sized for four warps) + block-table slices.
+  const size_t table_bytes = smem - static_cast<size_t>(kDecodeWarps) * G * (D + 2) * sizeof(float);
+  const int warps = mma_warps_per_cta(static_cast<int64_t>(p.splits) * p.Hkv * p.B);
+  if (p.mods.n > 0) {
+    return warps == 2 ? launch_decode_mma_w<D, PAGED, true, 2>(p, G, st, table_bytes)
+                      : launch_decode_mma_w<D, PAGED, true, 4>(p, G, st, table_bytes);
+  }
+  return warps == 2 ? launch_decode_mma_w<D, PAGED, false, 2>(p, G, st, table_bytes)
+                    : launch_decode_mma_w<D, PAGED, false, 4>(p, G, st, table_bytes);
 }
 
 // Dense caches with one or two query rows per kv head stay on the FMA kernel (it already

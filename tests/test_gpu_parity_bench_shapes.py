@@ -107,7 +107,8 @@ def test_kv_append_is_bit_exact_and_round_trips(P, D, T):
     vp = randn_bf16(n_pages, P, Hkv, D, seed=2)
     kn = randn_bf16(B, Hkv, T, D, seed=3)
     vn = randn_bf16(B, Hkv, T, D, seed=4)
-    pos = torch.tensor([0, 5, min(P * blocks - T, 17)], dtype=torch.int32)
+    cap = P * blocks                                   # tokens a sequence's table can hold
+    pos = torch.tensor([0, min(5, cap - T), min(cap - T, 17)], dtype=torch.int32)
     kpd, vpd, td = kp.to(DEV), vp.to(DEV), table.to(DEV)
     st = F.new_status(DEV)
     F.kv_append(kn.to(DEV), vn.to(DEV), kpd, vpd, td, seq_pos=pos.to(DEV), status=st)
