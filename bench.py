@@ -247,7 +247,7 @@ def softcap_mods(w):
 class Runner:
     """Launches one workload once per call through the C ABI on fixed device buffers."""
 
-    def __init__(self, w, inputs, q_scale: float = 1.0):
+    def __init__(self, w, inputs, q_scale: float = 1.0, sm_margin: int = 0):
         from loopfuse_b200 import _native, functional as F, spec as S
         self.w = w
         scale = w.D ** -0.5
@@ -258,7 +258,7 @@ class Runner:
             kind = S.MASK_CAUSAL_WINDOW if w.window else S.MASK_CAUSAL
             self.out = torch.empty_like(q)
             prep = F.PreparedPrefill(q, k, v, scale=scale, mods=softcap_mods(w), mask_kind=kind,
-                                     window=w.window, out=self.out)
+                                     window=w.window, out=self.out, sm_margin=sm_margin)
             self.launch = prep.run
             self.launches_per_call = 1
             return
@@ -467,8 +467,12 @@ def run_ours(args, workload) -> None:
     if world > 1 and not args.kernel_only:
         # ---- the path's one collective: all-gather of the output slabs, once per step, on a
         # second stream: the gather of step i overlaps the kernel of step i+1.
+        # (With one CTA of the persistent prefill kernel resident on every SM the collective's
+        # kernel cannot start before it ends, so the two serialise. `--sm-margin` leaves SMs
+        # free, but NCCL's all-gather needs ~26 of them for its full rate: not worth it.)
         comm = torch.cuda.Stream(dev)
         cur = torch.cuda.current_stream(dev)
+        piped = [Runner(w, s, sm_margin=args.sm_margin) for s in sets] if args.sm_margin else runners
         full_shape = (world * w.B, *runners[0].out.shape[1:])
         gathered = [torch.empty(full_shape, dtype=torch.bfloat16, device=dev) for _ in range(2)]
         ev_k = [torch.cuda.Event() for _ in range(2)]
@@ -479,11 +483,11 @@ def run_ours(args, workload) -> None:
                 k = i % 2
                 if i >= 2:
                     cur.wait_event(ev_g[k])       # gather i-2 has read out[k]
-                runners[k].launch()
+                piped[k].launch()
                 ev_k[k].record(cur)
                 with torch.cuda.stream(comm):
                     comm.wait_event(ev_k[k])
-                    sharding.gather_output(runners[k].out, full_shape, out=gathered[k])
+                    sharding.gather_output(piped[k].out, full_shape, out=gathered[k])
                     ev_g[k].record(comm)
             cur.wait_stream(comm)
 
@@ -500,7 +504,7 @@ def run_ours(args, workload) -> None:
         s2, e2 = events()
         s2.record()
         for i in range(steps):
-            sharding.gather_output(runners[i % 2].out, full_shape, out=gathered[i % 2])
+            sharding.gather_output(piped[i % 2].out, full_shape, out=gathered[i % 2])
         e2.record()
         barrier()
         overlapped_ms, gather_ms = max_over_ranks(
@@ -513,7 +517,7 @@ def run_ours(args, workload) -> None:
         slabs = gathered[last].view(world, -1).view(torch.int16).to(torch.int64)
         weights = torch.arange(slabs.shape[1], device=dev, dtype=torch.int64) % 8191 + 1
         got = (slabs * weights).sum(dim=1)
-        mine = (runners[last].out.reshape(-1).view(torch.int16).to(torch.int64) * weights).sum()
+        mine = (piped[last].out.reshape(-1).view(torch.int16).to(torch.int64) * weights).sum()
         all_mine = torch.empty(world, dtype=torch.int64, device=dev)
         dist.all_gather_into_tensor(all_mine, mine.reshape(1))
         slab_bytes = runners[0].out.numel() * 2
@@ -523,6 +527,7 @@ def run_ours(args, workload) -> None:
             "gather_ms_per_step": gather_ms, "overlapped_ms_per_step": overlapped_ms,
             "gather_bus_gbs": slab_bytes * (world - 1) / 1e9 / (gather_ms * 1e-3),
             "gather_verified": bool(torch.equal(got, all_mine)),
+            "sm_margin": args.sm_margin,
         })
         collective = ("one all-gather of the output slabs per step on a second stream, "
                       "overlapping the next step's kernel; `value` = whole-job rate of that "
@@ -689,6 +694,11 @@ def main() -> None:
     ap.add_argument("--workload", default="causal_softcap")
     ap.add_argument("--batch", type=int, default=0,
                     help="override the batch per GPU (small cases for profiler captures)")
+    ap.add_argument("--sm-margin", type=int, default=0,
+                    help="SMs the prefill kernel leaves to the collective in the pipelined "
+                         "multi-GPU loop (0: none - NCCL's all-gather moves ~16 GB/s per CTA "
+                         "and needs about 26 SMs for the full NVLink rate, which costs the "
+                         "kernel more than the overlap returns: measured)")
     ap.add_argument("--no-others", action="store_true",
                     help="skip the figures for the other configurations")
     ap.add_argument("--kernel-only", action="store_true",

@@ -107,6 +107,9 @@ typedef struct {
                            iterated (bit-exact check against lf_skip_range) */
   int32_t kv_tile;      /* 0 = the library picks; 64 or 128 pins the KV tile of the kernel
                            (128 exists only for the bounded-softcap kernel) */
+  int32_t sm_margin;    /* persistent kernels only: leave this many SMs without a CTA, for
+                           kernels that must run at the same time (a collective on another
+                           stream cannot start while one CTA per SM is resident); 0 = use all */
 } LfPrefillArgs;
 
 typedef struct {

@@ -34,6 +34,7 @@ class LfPrefillArgs(C.Structure):
         ("mod_op", C.c_int32 * LF_MAX_MODS), ("mod_arg", C.c_float * LF_MAX_MODS),
         ("mask_kind", C.c_int32), ("window", C.c_int32), ("causal_offset", C.c_int32),
         ("status", C.c_void_p), ("dbg_ranges", C.c_void_p), ("kv_tile", C.c_int32),
+        ("sm_margin", C.c_int32),
     ]
 
 

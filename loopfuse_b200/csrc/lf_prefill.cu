@@ -93,6 +93,7 @@ struct PrefillParams {
   int32_t n_pairs;       // query-tile pairs per head
   int32_t n_items;       // n_pairs * Hq * B
   unsigned int* ticket;  // device counter, zero at launch
+  int32_t sm_margin;     // SMs left without a CTA
 };
 
 // Barrier block at the start of shared memory.
@@ -842,7 +843,8 @@ static int launch_prefill_bounded(const CUtensorMap& mq, const CUtensorMap& mk,
     set_cuda_error(e, "cudaMemsetAsync(ticket)");
     return LF_ERR_CUDA;
   }
-  const int grid = static_cast<int>(n_items < sm_count ? n_items : sm_count);
+  const int ctas = sm_count - p.sm_margin > 0 ? sm_count - p.sm_margin : 1;
+  const int grid = static_cast<int>(n_items < ctas ? n_items : ctas);
   prefill_bounded_kernel<D><<<grid, kBoundedThreads, smem, st>>>(mq, mk, mv, mo, p);
   return check_launch("prefill_bounded_kernel");
 }
@@ -883,7 +885,8 @@ static int launch_prefill_wide(const CUtensorMap& mq, const CUtensorMap& mk,
     set_cuda_error(e, "cudaMemsetAsync(ticket)");
     return LF_ERR_CUDA;
   }
-  const int grid = static_cast<int>(n_items < sm_count ? n_items : sm_count);
+  const int ctas = sm_count - p.sm_margin > 0 ? sm_count - p.sm_margin : 1;
+  const int grid = static_cast<int>(n_items < ctas ? n_items : ctas);
   prefill_wide_kernel<D><<<grid, kWideThreads, smem, st>>>(mq, mk, mv, mo, p);
   return check_launch("prefill_wide_kernel");
 }
@@ -934,6 +937,8 @@ static int prefill_impl(const LfPrefillArgs* a, void* const* launch) {
   p.n_pairs = 0;
   p.n_items = 0;
   p.ticket = nullptr;
+  if (a->sm_margin < 0) return LF_ERR_INVALID_ARG;
+  p.sm_margin = a->sm_margin;
   p.mods.n = 0;
   for (int i = 0; i < LF_MAX_MODS; ++i) {
     p.mods.op[i] = 0;

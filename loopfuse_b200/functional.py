@@ -73,12 +73,14 @@ def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scal
                       out: Optional[torch.Tensor] = None,
                       status: Optional[torch.Tensor] = None,
                       dbg_ranges: Optional[torch.Tensor] = None,
-                      kv_tile: int = 0) -> torch.Tensor:
+                      kv_tile: int = 0, sm_margin: int = 0) -> torch.Tensor:
     """softmax(mask(mods(scale * q k^T))) v for q [B,Hq,Sq,D], k/v [B,Hkv,Skv,D] (bf16).
 
-    ``kv_tile`` pins the KV tile of the kernel (64 or 128 keys; 0 lets the library choose)."""
+    ``kv_tile`` pins the KV tile of the kernel (64 or 128 keys; 0 lets the library choose);
+    ``sm_margin`` leaves that many SMs free of the persistent kernels' CTAs (for a collective
+    that runs at the same time on another stream)."""
     a, out, dev = _prefill_args(q, k, v, scale, mods, mask_kind, window, causal_offset, out,
-                                status, dbg_ranges, kv_tile)
+                                status, dbg_ranges, kv_tile, sm_margin)
     with torch.cuda.device(dev):
         rc = _native.load().lf_prefill_bf16(C.byref(a), _stream_ptr(dev))
     _native.check(rc, "lf_prefill_bf16")
@@ -96,9 +98,11 @@ class PreparedPrefill:
     def __init__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float = 1.0,
                  mods: Sequence[ScoreMod] = (), mask_kind: int = MASK_NONE, window: int = 0,
                  causal_offset: int = 0, out: Optional[torch.Tensor] = None,
-                 status: Optional[torch.Tensor] = None, kv_tile: int = 0) -> None:
+                 status: Optional[torch.Tensor] = None, kv_tile: int = 0,
+                 sm_margin: int = 0) -> None:
         self._args, self.out, self._dev = _prefill_args(
-            q, k, v, scale, mods, mask_kind, window, causal_offset, out, status, None, kv_tile)
+            q, k, v, scale, mods, mask_kind, window, causal_offset, out, status, None, kv_tile,
+            sm_margin)
         self._keep = (q, k, v, status)
         self._fn = _native.load().lf_prefill_bf16
         self._ref = C.byref(self._args)
@@ -126,7 +130,7 @@ def prefill_kv_tile(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale:
     """KV tile size (64 or 128 keys) of the kernel ``prefill_attention`` runs for these
     arguments; skip ranges and ``dbg_ranges`` are in units of it."""
     a, _, _ = _prefill_args(q, k, v, scale, mods, mask_kind, window, causal_offset, q,
-                            None, None, kv_tile)
+                            None, None, kv_tile, 0)
     rc = _native.load().lf_prefill_kv_tile(C.byref(a))
     if rc < 0:
         _native.check(rc, "lf_prefill_kv_tile")
@@ -134,7 +138,7 @@ def prefill_kv_tile(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale:
 
 
 def _prefill_args(q, k, v, scale, mods, mask_kind, window, causal_offset, out, status,
-                  dbg_ranges, kv_tile):
+                  dbg_ranges, kv_tile, sm_margin=0):
     dev = _require_cuda(q, k, v)
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
         _check_bf16_lastdim(t, n)
@@ -168,6 +172,7 @@ def _prefill_args(q, k, v, scale, mods, mask_kind, window, causal_offset, out, s
             raise ValueError(f"dbg_ranges must be a CUDA int32 tensor with >= {need} elements")
         a.dbg_ranges = dbg_ranges.data_ptr()
     a.kv_tile = int(kv_tile)
+    a.sm_margin = int(sm_margin)
     return a, out, dev
 
 
