@@ -41,7 +41,7 @@
 extern "C" {
 #endif
 
-#define LF_ABI_VERSION 2
+#define LF_ABI_VERSION 3
 
 typedef enum {
   LF_OK = 0,
@@ -107,6 +107,17 @@ typedef struct {
                            iterated (bit-exact check against lf_skip_range) */
   int32_t kv_tile;      /* 0 = the library picks; 64 or 128 pins the KV tile of the kernel
                            (128 exists only for the bounded-softcap kernel) */
+  /* Paged K and / or V (NULL tables = dense operands). With k_block_table, `k` is a pool
+   * [n_pages, page_size, Hkv, D] and k_stride its element strides of (page, slot, kv head);
+   * key t of sequence b is pool[k_block_table[b, t / page_size], t % page_size, kv head, :]
+   * for t < Skv. Likewise v_block_table / v / v_stride. The gather is fused into the tile load
+   * of the kernel (the reference's two-level load, loopfuse/codegen.py:738-872); an entry
+   * outside [0, n_pages) is reported as LF_DEV_BAD_PAGE in `status` and read as page 0. */
+  const int32_t* k_block_table; /* int32 [B, >= ceil(Skv / page_size)] */
+  const int32_t* v_block_table;
+  int64_t bt_stride;            /* elements between rows of the tables */
+  int32_t page_size;
+  int32_t n_pages;
   int32_t sm_margin;    /* persistent kernels only: leave this many SMs without a CTA, for
                            kernels that must run at the same time (a collective on another
                            stream cannot start while one CTA per SM is resident); 0 = use all */
@@ -244,6 +255,15 @@ int lf_paged_gather_bf16(const void* pool, const int32_t* block_table, void* out
                          int32_t Hkv, int32_t Skv, int32_t D, int32_t page_size, int32_t n_pages,
                          const int64_t* pool_stride, int64_t bt_stride, int32_t* status,
                          void* stream);
+
+/* Self-test of the bounded device-side waits (no counterpart in the reference, whose kernels
+ * have no cross-warp waits): a one-thread kernel waits at most `limit_cycles` SM clocks on an
+ * mbarrier that nobody arrives on, then records LF_DEV_TIMEOUT | (99 << 8) in `status` (device
+ * word, required) and the clocks it really waited in `waited_cycles` (device int64, optional),
+ * and returns. Shows on a live GPU what every kernel of the library does when a wait does not
+ * complete: give up, report, terminate normally. limit_cycles in (0, 2e9]. */
+int lf_selftest_wait_timeout(int64_t limit_cycles, int32_t* status, int64_t* waited_cycles,
+                             void* stream);
 
 /* Append to a paged KV cache: new token i of sequence b (logical position pos = seq_pos[b] + i,
  * or start_pos + i) is written to

@@ -17,7 +17,7 @@ EXPORTS = [
     "lf_decode_bf16", "lf_decode_paged_bf16", "lf_decode_auto_splits",
     "lf_decode_workspace_bytes", "lf_combine_f32", "lf_paged_gather_bf16",
     "lf_decode_bf16_static", "lf_prefill_kv_tile", "lf_tile_map_cache_stats",
-    "lf_kv_append_bf16",
+    "lf_kv_append_bf16", "lf_selftest_wait_timeout",
 ]
 
 LF_STATIC_SCRATCH_BYTES = 8 << 20
@@ -34,6 +34,8 @@ class LfPrefillArgs(C.Structure):
         ("mod_op", C.c_int32 * LF_MAX_MODS), ("mod_arg", C.c_float * LF_MAX_MODS),
         ("mask_kind", C.c_int32), ("window", C.c_int32), ("causal_offset", C.c_int32),
         ("status", C.c_void_p), ("dbg_ranges", C.c_void_p), ("kv_tile", C.c_int32),
+        ("k_block_table", C.c_void_p), ("v_block_table", C.c_void_p), ("bt_stride", C.c_int64),
+        ("page_size", C.c_int32), ("n_pages", C.c_int32),
         ("sm_margin", C.c_int32),
     ]
 
@@ -102,6 +104,8 @@ def load() -> C.CDLL:
     lib.lf_tile_map_cache_stats.restype = None
     lib.lf_kv_append_bf16.argtypes = [C.POINTER(LfKvAppendArgs), C.c_void_p]
     lib.lf_kv_append_bf16.restype = C.c_int
+    lib.lf_selftest_wait_timeout.argtypes = [C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.lf_selftest_wait_timeout.restype = C.c_int
     lib.lf_skip_range.argtypes = [C.c_int32] * 8 + [C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     lib.lf_skip_range.restype = None
     for name in ("lf_decode_bf16", "lf_decode_paged_bf16", "lf_decode_bf16_static"):

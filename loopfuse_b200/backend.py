@@ -44,7 +44,7 @@ _DECODE_GROUPS = (1, 2, 4, 8)
 class AttentionPlan:
     """A spec bound to concrete sizes: which kernel runs, with which parameters."""
     spec: AttentionSpec
-    kernel: str                 # "prefill" | "decode" | "paged_decode" | "paged_gather+prefill"
+    kernel: str                 # "prefill" | "paged_prefill" | "decode" | "paged_decode"
     B: int
     Hq: int
     Hkv: int
@@ -158,7 +158,7 @@ class CompiledAttention:
         if is_decode:
             kernel = "paged_decode" if both_paged else "decode"
         else:
-            kernel = "paged_gather+prefill" if (spec.k.paged or spec.v.paged) else "prefill"
+            kernel = "paged_prefill" if (spec.k.paged or spec.v.paged) else "prefill"
         return AttentionPlan(spec, kernel, B, Hq, Hkv, Sq, Skv, D, scale, mods, window, page_size,
                              spec.mask_kind)
 
@@ -224,22 +224,17 @@ class CompiledAttention:
                     status=status)
             self._check(status, plan)
             return (out,)
-        # Prefill. A paged operand is gathered into a dense [B, Hkv, S, D] tensor first (the
-        # gather kernel applies the same page-index rule as the decode kernels); K and V may be
-        # paged independently, as in the reference's own paged-attention tests
-        # (tests/test_accuracy.py:253-311: K through paged_load, V dense).
-        if spec.k.paged:
-            k = F.paged_gather(args[spec.k.placeholder], args[spec.k.block_table], status=status)
-        else:
-            k = args[spec.k.placeholder]
-        if spec.v.paged:
-            v = F.paged_gather(args[spec.v.placeholder], args[spec.v.block_table], status=status)
-        else:
-            v = args[spec.v.placeholder]
+        # Prefill. K and V may be paged independently, as in the reference's own paged-attention
+        # tests (tests/test_accuracy.py:253-311: K through paged_load, V dense); the gather of a
+        # paged operand is fused into the kernel's tile loads.
         if spec.k.paged or spec.v.paged:
-            out = F.prefill_attention(q, k, v, scale=plan.scale, mods=plan.mods,
-                                      mask_kind=spec.mask_kind, window=plan.window, status=status)
+            out = F.prefill_attention(
+                q, args[spec.k.placeholder], args[spec.v.placeholder], scale=plan.scale,
+                mods=plan.mods, mask_kind=spec.mask_kind, window=plan.window, status=status,
+                k_block_table=args[spec.k.block_table] if spec.k.paged else None,
+                v_block_table=args[spec.v.block_table] if spec.v.paged else None)
         else:
+            k, v = args[spec.k.placeholder], args[spec.v.placeholder]
             out = torch.empty((plan.B, plan.Hq, plan.Sq, plan.D), dtype=q.dtype, device=q.device)
             self._prepared_prefill(plan, q, k, v, status).run(out)
         self._check(status, plan)

@@ -21,9 +21,34 @@ int check_launch(const char* where) {
   return LF_ERR_CUDA;
 }
 
+// Self-test of the bounded device-side wait: one thread waits, with a caller-given short limit,
+// on an mbarrier that nobody ever arrives on. The wait runs out, the kernel records
+// LF_DEV_TIMEOUT | (site 99 << 8) in the status word and returns normally - the same way every
+// kernel of the library reacts to a wait that does not complete (nothing traps, nothing spins
+// for ever, the context stays usable).
+__global__ void selftest_wait_kernel(long long limit_cycles, int32_t* status, long long* waited) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+    const long long t0 = clock64();
+    const bool ok = mbar_wait(&bar, 0, limit_cycles);
+    if (waited) *waited = clock64() - t0;
+    if (!ok && status) atomicCAS(status, LF_DEV_OK, LF_DEV_TIMEOUT | (99 << 8));
+  }
+}
+
 }  // namespace lf
 
 extern "C" {
+
+int lf_selftest_wait_timeout(int64_t limit_cycles, int32_t* status, int64_t* waited_cycles,
+                             void* stream) {
+  if (limit_cycles <= 0 || limit_cycles > 2000000000ll || !status) return LF_ERR_INVALID_ARG;
+  lf::selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      limit_cycles, status, reinterpret_cast<long long*>(waited_cycles));
+  return lf::check_launch("selftest_wait_kernel");
+}
 
 const char* lf_strerror(int status) {
   switch (status) {

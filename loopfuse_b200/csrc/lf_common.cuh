@@ -229,12 +229,13 @@ constexpr long long kWaitLimitCycles = 400000000ll;
 
 // Bounded wait. Returns false when the limit ran out: the caller records a status code and
 // leaves its role loop, so the kernel still terminates and frees its tensor memory.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
+                                          long long limit_cycles = kWaitLimitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t it = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++it & 7u) == 0u && clock64() - t0 > kWaitLimitCycles) return false;
+    if ((++it & 7u) == 0u && clock64() - t0 > limit_cycles) return false;
   }
   return true;
 }

@@ -94,6 +94,16 @@ struct PrefillParams {
   int32_t n_items;       // n_pairs * Hq * B
   unsigned int* ticket;  // device counter, zero at launch
   int32_t sm_margin;     // SMs left without a CTA
+  // Paged K and / or V (prefill_kernel only): pools [n_pages, page_size, Hkv, D] read through a
+  // block table; bit 0 of `paged`: K, bit 1: V.
+  int32_t paged;
+  const __nv_bfloat16* k_pool;
+  const __nv_bfloat16* v_pool;
+  const int32_t* k_table;
+  const int32_t* v_table;
+  int64_t kp_stride[3], vp_stride[3];  // (page, slot, kv head)
+  int64_t bt_stride;
+  int32_t page_size, page_shift, n_pages;
 };
 
 // Barrier block at the start of shared memory.
@@ -173,7 +183,8 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     mbar_init(&bars->q_full[0], 1);
     mbar_init(&bars->q_full[1], 1);
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&bars->kv_full[s], 1);
+      // (paged operands: one arrival for the TMA part, one for the warp's own copies)
+      mbar_init(&bars->kv_full[s], p.paged ? 2 : 1);
       mbar_init(&bars->kv_empty[s], 2);
     }
     for (int t = 0; t < 2; ++t) {
@@ -200,7 +211,126 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
 
-  if (warp == kProducerWarp) {
+  if (warp == kProducerWarp && p.paged) {
+    // ---------------- producer with a paged K and / or V ----------------
+    // The two-level load of the reference (loopfuse/codegen.py:738-872: read tile_K table
+    // entries, then gather the rows) fused into the tile load: a dense operand still arrives by
+    // TMA; a paged one is copied by the whole warp, row by row, with 16-byte cp.async straight
+    // from the pool into the 128-byte-swizzled tile layout the MMA descriptors read (16-byte
+    // piece c of row r of a 64-column block sits at piece c ^ (r & 7)). Rows past Skv are
+    // zero-filled, like TMA does. Copies of up to kLag stages are in flight; a stage is
+    // published (second arrival on its full barrier) when its copies have landed and a proxy
+    // fence has made them visible to the tensor pipe.
+    constexpr int kLag = 2;
+    constexpr int kChunks = D / 8;            // 16-byte pieces per row
+    constexpr int kRowsPerPass = 32 / kChunks;  // rows one pass of the warp covers
+    const bool elected = elect_one_sync();
+    if (elected) {
+      for (int t = 0; t < 2; ++t) {
+        if (!has_work[t]) continue;
+        mbar_arrive_expect_tx(&bars->q_full[t], kQTileBytes);
+#pragma unroll
+        for (int kb = 0; kb < kBlocksD; ++kb)
+          tma_load_4d(sQ + t * kQTileBytes + kb * kQBlockBytes, &tmap_q, &bars->q_full[t],
+                      kb * 64, (iq0 + t) * kTileQ, h, b);
+      }
+    }
+    __syncwarp();
+    int n = 0;
+    int published = 0;  // stages whose copies have been published
+    bool ok = true;
+    auto page_of = [&](int t) { return p.page_shift >= 0 ? (t >> p.page_shift) : (t / p.page_size); };
+    // Copy the 64 rows of KV tile j of a paged operand into `dst`.
+    auto copy_tile = [&](bool is_v, int j, unsigned char* dst) {
+      const __nv_bfloat16* pool = is_v ? p.v_pool : p.k_pool;
+      const int32_t* table = (is_v ? p.v_table : p.k_table) + static_cast<int64_t>(b) * p.bt_stride;
+      const int64_t* st = is_v ? p.vp_stride : p.kp_stride;
+      // Lane l looks up the pages of rows l and l + 32; the others get them by shuffle.
+      int64_t row_off[2];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int t = j * kTileK + half * 32 + lane;
+        row_off[half] = -1;
+        if (t < p.Skv) {
+          const int pg_idx = page_of(t);
+          int32_t pg = table[pg_idx];
+          if (pg < 0 || pg >= p.n_pages) {
+            if (p.status) atomicExch(p.status, LF_DEV_BAD_PAGE);
+            pg = 0;
+          }
+          row_off[half] = pg * st[0] + (t - pg_idx * p.page_size) * st[1] + hkv * st[2];
+        }
+      }
+      const int c = lane % kChunks;
+      const uint32_t dst_u32 = smem_u32(dst) + (c / 8) * kKVBlockBytes;
+#pragma unroll
+      for (int pass = 0; pass < kTileK / kRowsPerPass; ++pass) {
+        const int r = pass * kRowsPerPass + lane / kChunks;
+        const int64_t off_lo = __shfl_sync(0xffffffffu, row_off[0], r & 31);
+        const int64_t off_hi = __shfl_sync(0xffffffffu, row_off[1], r & 31);
+        const int64_t off = r < 32 ? off_lo : off_hi;
+        const uint32_t d = dst_u32 + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+        const __nv_bfloat16* src = pool + (off >= 0 ? off : 0) + c * 8;
+        const uint32_t nbytes = off >= 0 ? 16u : 0u;  // 0: the 16 bytes are zero-filled
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src),
+                     "r"(nbytes)
+                     : "memory");
+      }
+    };
+    auto publish_up_to = [&](int upto) {  // publish stages [published, upto)
+      if (published < upto) {
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0)
+          for (int i = published; i < upto; ++i) mbar_arrive(&bars->kv_full[i % kStages]);
+        published = upto;
+      }
+    };
+    // ja: tile of `first_is_v ? V : K`; jb >= 0: a K tile in the second half of the stage.
+    auto load_pair = [&](bool first_is_v, int ja, int jb) {
+      if (!ok) return;
+      const int stage = n % kStages;
+      const uint32_t parity = ((n / kStages) & 1) ^ 1;
+      if (!mbar_wait(&bars->kv_empty[stage], parity)) {
+        report_timeout(p.status, 1);
+        ok = false;
+        return;
+      }
+      unsigned char* dst = sKV + stage * (2 * kKVTileBytes);
+      const bool a_paged = (p.paged >> (first_is_v ? 1 : 0)) & 1;
+      const bool b_paged = jb >= 0 && (p.paged & 1);
+      if (elected) {
+        const uint32_t tx = (a_paged ? 0u : kKVTileBytes) + ((jb >= 0 && !b_paged) ? kKVTileBytes : 0u);
+        if (tx) mbar_arrive_expect_tx(&bars->kv_full[stage], tx);
+        else mbar_arrive(&bars->kv_full[stage]);
+        if (!a_paged) {
+#pragma unroll
+          for (int kb = 0; kb < kBlocksD; ++kb)
+            tma_load_4d(dst + kb * kKVBlockBytes, first_is_v ? &tmap_v : &tmap_k,
+                        &bars->kv_full[stage], kb * 64, ja * kTileK, hkv, b);
+        }
+        if (jb >= 0 && !b_paged) {
+#pragma unroll
+          for (int kb = 0; kb < kBlocksD; ++kb)
+            tma_load_4d(dst + kKVTileBytes + kb * kKVBlockBytes, &tmap_k, &bars->kv_full[stage],
+                        kb * 64, jb * kTileK, hkv, b);
+        }
+      }
+      __syncwarp();
+      if (a_paged) copy_tile(first_is_v, ja, dst);
+      if (b_paged) copy_tile(false, jb, dst + kKVTileBytes);
+      cp_async_commit();  // one group per stage, empty or not
+      ++n;
+      cp_async_wait<kLag>();  // the copies of every stage but the last kLag have landed
+      publish_up_to(n - kLag);
+    };
+    if (hi > lo) {
+      load_pair(false, lo, lo + 1 < hi ? lo + 1 : -1);
+      for (int j = lo; j < hi; ++j) load_pair(true, j, j + 2 < hi ? j + 2 : -1);
+    }
+    cp_async_wait<0>();
+    publish_up_to(n);
+  } else if (warp == kProducerWarp) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       for (int t = 0; t < 2; ++t) {
@@ -939,6 +1069,30 @@ static int prefill_impl(const LfPrefillArgs* a, void* const* launch) {
   p.ticket = nullptr;
   if (a->sm_margin < 0) return LF_ERR_INVALID_ARG;
   p.sm_margin = a->sm_margin;
+  // Paged operands: `k` / `v` is then a pool [n_pages, page_size, Hkv, D] with strides (page,
+  // slot, kv head), read through its block table.
+  p.paged = (a->k_block_table ? 1 : 0) | (a->v_block_table ? 2 : 0);
+  p.k_pool = static_cast<const __nv_bfloat16*>(a->k);
+  p.v_pool = static_cast<const __nv_bfloat16*>(a->v);
+  p.k_table = a->k_block_table;
+  p.v_table = a->v_block_table;
+  for (int i = 0; i < 3; ++i) {
+    p.kp_stride[i] = a->k_stride[i];
+    p.vp_stride[i] = a->v_stride[i];
+  }
+  p.bt_stride = a->bt_stride;
+  p.page_size = a->page_size;
+  p.page_shift = -1;
+  p.n_pages = a->n_pages;
+  if (p.paged) {
+    if (a->page_size <= 0 || a->n_pages <= 0) return LF_ERR_INVALID_ARG;
+    if (a->bt_stride < (a->Skv + a->page_size - 1) / a->page_size) return LF_ERR_INVALID_ARG;
+    for (int sh = 0; sh < 31; ++sh)
+      if ((1 << sh) == a->page_size) p.page_shift = sh;
+    for (int i = 0; i < 3; ++i)
+      if (((p.paged & 1) && a->k_stride[i] % 8) || ((p.paged & 2) && a->v_stride[i] % 8))
+        return LF_ERR_ALIGNMENT;
+  }
   p.mods.n = 0;
   for (int i = 0; i < LF_MAX_MODS; ++i) {
     p.mods.op[i] = 0;
@@ -973,7 +1127,10 @@ static int prefill_impl(const LfPrefillArgs* a, void* const* launch) {
         p.c2 = post * kLog2eF;
         // |logit2| <= c2: small enough for the fixed softmax reference (the row sum of up to
         // 2^22 terms of at most 2^80 stays far below the fp32 limit).
-        mode = (p.c2 <= kBoundedMaxC2 && a->Skv <= (1 << 22)) ? kModeBounded : kModeSoftcap;
+        // (the fixed-reference kernels read dense K/V; a paged operand goes to the running-max
+        // kernel, whose producer warp can gather)
+        mode = (p.c2 <= kBoundedMaxC2 && a->Skv <= (1 << 22) && !p.paged) ? kModeBounded
+                                                                           : kModeSoftcap;
         const float a2 = p.a * p.a, k0 = p.a * p.c2;
         p.qc[0] = k0;
         p.qc[1] = k0 * a2 * (-1.f / 3.f);
@@ -1001,10 +1158,18 @@ static int prefill_impl(const LfPrefillArgs* a, void* const* launch) {
   CUtensorMap mq, mk, mv;
   int rc = make_tile_map(&mq, a->q, a->B, a->Hq, a->Sq, a->D, a->q_stride, kTileQ);
   if (rc != LF_OK) return rc;
-  rc = make_tile_map(&mk, a->k, a->B, a->Hkv, a->Skv, a->D, a->k_stride, kv_tile);
-  if (rc != LF_OK) return rc;
-  rc = make_tile_map(&mv, a->v, a->B, a->Hkv, a->Skv, a->D, a->v_stride, kv_tile);
-  if (rc != LF_OK) return rc;
+  if (p.paged & 1) {
+    mk = mq;  // never used: the producer warp gathers K itself
+  } else {
+    rc = make_tile_map(&mk, a->k, a->B, a->Hkv, a->Skv, a->D, a->k_stride, kv_tile);
+    if (rc != LF_OK) return rc;
+  }
+  if (p.paged & 2) {
+    mv = mq;
+  } else {
+    rc = make_tile_map(&mv, a->v, a->B, a->Hkv, a->Skv, a->D, a->v_stride, kv_tile);
+    if (rc != LF_OK) return rc;
+  }
 
   CUtensorMap mo;  // output store boxes of the persistent kernels: 32 rows x 32 columns
   if (mode == kModeBounded) {

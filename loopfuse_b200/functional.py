@@ -73,14 +73,23 @@ def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scal
                       out: Optional[torch.Tensor] = None,
                       status: Optional[torch.Tensor] = None,
                       dbg_ranges: Optional[torch.Tensor] = None,
-                      kv_tile: int = 0, sm_margin: int = 0) -> torch.Tensor:
+                      kv_tile: int = 0, sm_margin: int = 0,
+                      k_block_table: Optional[torch.Tensor] = None,
+                      v_block_table: Optional[torch.Tensor] = None,
+                      seq_len: Optional[int] = None) -> torch.Tensor:
     """softmax(mask(mods(scale * q k^T))) v for q [B,Hq,Sq,D], k/v [B,Hkv,Skv,D] (bf16).
+
+    With ``k_block_table`` (``v_block_table``), ``k`` (``v``) is a paged pool
+    ``[pages, page_size, Hkv, D]`` (or ``[pages, Hkv, D]``, one token per page) read through that
+    int32 table ``[B, blocks]``; the gather is fused into the kernel's tile loads. ``seq_len``
+    bounds the keys when the table covers more.
 
     ``kv_tile`` pins the KV tile of the kernel (64 or 128 keys; 0 lets the library choose);
     ``sm_margin`` leaves that many SMs free of the persistent kernels' CTAs (for a collective
     that runs at the same time on another stream)."""
     a, out, dev = _prefill_args(q, k, v, scale, mods, mask_kind, window, causal_offset, out,
-                                status, dbg_ranges, kv_tile, sm_margin)
+                                status, dbg_ranges, kv_tile, sm_margin, k_block_table,
+                                v_block_table, seq_len)
     with torch.cuda.device(dev):
         rc = _native.load().lf_prefill_bf16(C.byref(a), _stream_ptr(dev))
     _native.check(rc, "lf_prefill_bf16")
@@ -138,16 +147,40 @@ def prefill_kv_tile(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale:
 
 
 def _prefill_args(q, k, v, scale, mods, mask_kind, window, causal_offset, out, status,
-                  dbg_ranges, kv_tile, sm_margin=0):
+                  dbg_ranges, kv_tile, sm_margin=0, k_block_table=None, v_block_table=None,
+                  seq_len=None):
     dev = _require_cuda(q, k, v)
-    for t, n in ((q, "q"), (k, "k"), (v, "v")):
-        _check_bf16_lastdim(t, n)
-        if t.dim() != 4:
-            raise ValueError(f"{n} must be 4-D")
+    _check_bf16_lastdim(q, "q")
+    if q.dim() != 4:
+        raise ValueError("q must be 4-D")
     B, Hq, Sq, D = q.shape
-    Bk, Hkv, Skv, Dk = k.shape
-    if v.shape != k.shape or Bk != B or Dk != D:
-        raise ValueError(f"shape mismatch: q {tuple(q.shape)} k {tuple(k.shape)} v {tuple(v.shape)}")
+    tables = {}
+    Skv = None
+    keep = []
+    # A paged operand is a pool [pages, page_size, Hkv, D] (or [pages, Hkv, D]) plus its block
+    # table; a dense one is [B, Hkv, Skv, D].
+    for name, ten, table in (("k", k, k_block_table), ("v", v, v_block_table)):
+        if table is None:
+            _check_bf16_lastdim(ten, name)
+            if ten.dim() != 4 or ten.shape[0] != B or ten.shape[3] != D:
+                raise ValueError(f"shape mismatch: q {tuple(q.shape)} {name} {tuple(ten.shape)}")
+            tables[name] = (ten, None, ten.shape[1], ten.shape[2])
+        else:
+            pool = _pool_view(ten, name + " pool")
+            bt = _table_i32(table)
+            if not bt.is_cuda or bt.shape[0] != B or pool.shape[3] != D:
+                raise ValueError(f"{name}: pool {tuple(pool.shape)} / block table {tuple(bt.shape)} "
+                                 f"do not fit q {tuple(q.shape)}")
+            tables[name] = (pool, bt, pool.shape[2], bt.shape[1] * pool.shape[1])
+            keep.append(bt)
+    (kt, kbt, Hkv, Skv_k), (vt, vbt, Hkv_v, Skv_v) = tables["k"], tables["v"]
+    if Hkv != Hkv_v:
+        raise ValueError("k and v must have the same number of kv heads")
+    if kbt is None and vbt is None and Skv_k != Skv_v:
+        raise ValueError("k and v must have the same length")
+    Skv = seq_len if seq_len is not None else min(Skv_k, Skv_v)
+    if Skv > min(Skv_k, Skv_v) or Skv <= 0:
+        raise ValueError("seq_len exceeds what k / v hold")
     if Hq % Hkv:
         raise ValueError("Hq must be a multiple of Hkv")
     if out is None:
@@ -156,13 +189,26 @@ def _prefill_args(q, k, v, scale, mods, mask_kind, window, causal_offset, out, s
         _require_cuda(out)
         _check_bf16_lastdim(out, "out")
     a = _native.LfPrefillArgs()
-    a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    a.q, a.k, a.v, a.out = q.data_ptr(), kt.data_ptr(), vt.data_ptr(), out.data_ptr()
     a.B, a.Hq, a.Hkv, a.Sq, a.Skv, a.D = B, Hq, Hkv, Sq, Skv, D
     for i in range(3):
         a.q_stride[i] = q.stride(i)
-        a.k_stride[i] = k.stride(i)
-        a.v_stride[i] = v.stride(i)
+        a.k_stride[i] = kt.stride(i)
+        a.v_stride[i] = vt.stride(i)
         a.o_stride[i] = out.stride(i)
+    if kbt is not None or vbt is not None:
+        pools = [x for x, bt in ((kt, kbt), (vt, vbt)) if bt is not None]
+        bts = [bt for bt in (kbt, vbt) if bt is not None]
+        if len(pools) == 2 and pools[0].shape[:2] != pools[1].shape[:2]:
+            raise ValueError("paged k and v must share the page geometry")
+        if len(bts) == 2 and bts[0].stride(0) != bts[1].stride(0):
+            bts = [x.contiguous() for x in bts]
+            kbt, vbt = bts
+            keep += bts
+        a.k_block_table = kbt.data_ptr() if kbt is not None else None
+        a.v_block_table = vbt.data_ptr() if vbt is not None else None
+        a.bt_stride = bts[0].stride(0)
+        a.page_size, a.n_pages = pools[0].shape[1], pools[0].shape[0]
     _fill_mods(a, scale, mods)
     a.mask_kind, a.window, a.causal_offset = int(mask_kind), int(window), int(causal_offset)
     a.status = status.data_ptr() if status is not None else None
@@ -173,6 +219,7 @@ def _prefill_args(q, k, v, scale, mods, mask_kind, window, causal_offset, out, s
         a.dbg_ranges = dbg_ranges.data_ptr()
     a.kv_tile = int(kv_tile)
     a.sm_margin = int(sm_margin)
+    a._keep = keep   # (tables converted on the fly must outlive the launch)
     return a, out, dev
 
 

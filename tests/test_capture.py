@@ -130,7 +130,7 @@ def test_paged_prefill_goes_through_gather():
     kc = torch.randn(500, 4, 64, dtype=torch.bfloat16)
     kt = torch.randint(0, 500, (2, 160), dtype=torch.int32)
     plan = compile_plan(fn, (q, kc, kt, kc.clone()))
-    assert plan.kernel == "paged_gather+prefill" and plan.spec.mask_kind == S.MASK_CAUSAL
+    assert plan.kernel == "paged_prefill" and plan.spec.mask_kind == S.MASK_CAUSAL
 
 
 def test_generic_score_mods_are_captured_in_order():

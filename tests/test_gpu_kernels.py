@@ -479,3 +479,25 @@ def test_persistent_kernel_ticket_counters_wrap_around():
         F.prefill_attention(q, k, v, out=out, **kw)
         if i % 100 == 99:
             assert torch.equal(out, ref)
+
+
+def test_bounded_device_wait_runs_out_and_reports():
+    """A wait that can never complete (an mbarrier nobody arrives on) gives up after its limit,
+    writes LF_DEV_TIMEOUT into the status word and the kernel returns: check_status raises, the
+    context stays usable. The limit here is 2e5 clocks (~0.1 ms); the product kernels use the
+    same wait with a limit of 4e8 clocks."""
+    from loopfuse_b200 import _native
+    st = F.new_status(DEV)
+    waited = torch.zeros(1, dtype=torch.int64, device=DEV)
+    rc = _native.load().lf_selftest_wait_timeout(200_000, st.data_ptr(), waited.data_ptr(),
+                                                 torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(st.item()) == 1 | (99 << 8)
+    assert 200_000 <= int(waited.item()) < 400_000_000
+    with pytest.raises(RuntimeError, match="bounded device-side wait ran out .site 99"):
+        F.check_status(st)
+    # the context is alive: a real kernel runs and is correct afterwards
+    q, k, v = _prefill_case(1, 2, 2, 128, 128, 64)
+    out = _run_prefill(q, k, v, scale=0.125, mask_kind=S.MASK_CAUSAL)
+    assert max_err(out, O.attention_ref(q, k, v, scale=0.125, mask="causal")) <= TOL

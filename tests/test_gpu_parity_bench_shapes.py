@@ -232,3 +232,66 @@ def test_shard_units_on_device_concatenates_to_the_unsharded_result(world):
         ql, kl, vl = sharding.shard_units(qd, kd, vd, r, world)
         parts.append(F.decode_attention(ql, kl, vl, scale=wd.D ** -0.5, splits=2))
     assert torch.equal(torch.cat([p.reshape(-1) for p in parts]).view_as(full_d), full_d)
+
+
+# ------------------------------------------------------------------------------------------
+# paged K / V fused into the prefill tile loads
+# ------------------------------------------------------------------------------------------
+def _paged_prefill_case(B, Hq, Hkv, S_, D, P, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    blocks = -(-S_ // P)
+    n_pages = B * blocks + 9
+    q = randn_bf16(B, Hq, S_, D, seed=seed + 1)
+    kp = randn_bf16(n_pages, P, Hkv, D, seed=seed + 2)
+    vp = randn_bf16(n_pages, P, Hkv, D, seed=seed + 3)
+    kt = torch.randperm(n_pages, generator=g)[:B * blocks].view(B, blocks).to(torch.int32)
+    vt = torch.randperm(n_pages, generator=g)[:B * blocks].view(B, blocks).to(torch.int32)
+    return q, kp, vp, kt, vt
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,S_,D,P", [
+    (2, 4, 4, 384, 64, 1), (2, 8, 2, 593, 128, 16), (1, 4, 2, 300, 128, 12), (3, 4, 4, 128, 64, 16),
+])
+@pytest.mark.parametrize("which", ["k", "v", "kv"])
+def test_paged_prefill_fused_gather(B, Hq, Hkv, S_, D, P, which):
+    """K and / or V of a causal prefill read through a block table inside the kernel: equal, bit
+    for bit, to the same kernel on the gathered dense tensors (the gather only changes where the
+    rows come from), and within tolerance of the oracle."""
+    q, kp, vp, kt, vt = _paged_prefill_case(B, Hq, Hkv, S_, D, P)
+    k_dense = O.paged_kv_ref(kp, kt)[:, :, :S_].to(torch.bfloat16)
+    v_dense = O.paged_kv_ref(vp, vt)[:, :, :S_].to(torch.bfloat16)
+    qd = q.to(DEV)
+    kw = dict(scale=D ** -0.5, mask_kind=S.MASK_CAUSAL)
+    k_arg = kp.to(DEV) if "k" in which else k_dense.to(DEV)
+    v_arg = vp.to(DEV) if "v" in which else v_dense.to(DEV)
+    st = F.new_status(DEV)
+    out = F.prefill_attention(qd, k_arg, v_arg, status=st, seq_len=S_,
+                              k_block_table=kt.to(DEV) if "k" in which else None,
+                              v_block_table=vt.to(DEV) if "v" in which else None, **kw)
+    F.check_status(st)
+    dense = F.prefill_attention(qd, k_dense.to(DEV), v_dense.to(DEV), **kw)
+    assert torch.equal(out, dense)
+    want = O.attention_ref(q, k_dense, v_dense, mask="causal", batch_chunk=B)
+    assert max_err(out, want) <= TOL
+
+
+def test_paged_prefill_softcap_window_gqa_and_bad_page():
+    q, kp, vp, kt, vt = _paged_prefill_case(2, 8, 2, 700, 128, 16, seed=4)
+    k_dense = O.paged_kv_ref(kp, kt)[:, :, :700]
+    v_dense = O.paged_kv_ref(vp, vt)[:, :, :700]
+    st = F.new_status(DEV)
+    kw = dict(scale=128 ** -0.5, mods=SOFTCAP, mask_kind=S.MASK_CAUSAL_WINDOW, window=200,
+              seq_len=700, status=st)
+    out = F.prefill_attention(q.to(DEV), kp.to(DEV), vp.to(DEV), k_block_table=kt.to(DEV),
+                              v_block_table=vt.to(DEV), **kw)
+    F.check_status(st)
+    want = O.attention_ref(q, k_dense, v_dense, mods=O.softcap_mods(50.0), mask="window",
+                           window=200, batch_chunk=2)
+    assert max_err(out, want) <= TOL
+    bad = kt.clone()
+    bad[1, 5] = kp.shape[0] + 3
+    F.prefill_attention(q.to(DEV), kp.to(DEV), vp.to(DEV), k_block_table=bad.to(DEV),
+                        v_block_table=vt.to(DEV), **kw)
+    with pytest.raises(RuntimeError, match="page id"):
+        F.check_status(st)
+    torch.cuda.synchronize()
