@@ -41,7 +41,7 @@
 extern "C" {
 #endif
 
-#define LF_ABI_VERSION 3
+#define LF_ABI_VERSION 4
 
 typedef enum {
   LF_OK = 0,
@@ -121,6 +121,15 @@ typedef struct {
   int32_t sm_margin;    /* persistent kernels only: leave this many SMs without a CTA, for
                            kernels that must run at the same time (a collective on another
                            stream cannot start while one CTA per SM is resident); 0 = use all */
+  /* Additive score bias (NULL = none): bf16 [B, Hq, Sq, Skv], innermost stride 1, 16-byte
+   * aligned rows; bias_stride = element strides of (b, h, row). It is added to the score after
+   * the first `bias_pos` ops of the mod chain (0 <= bias_pos <= n_mod) and before the mask:
+   *     s = mod[bias_pos .. n_mod)( mod[0 .. bias_pos)(scale * q.k) + bias[b, h, i, j] )
+   * - the `QK * c + scores_bias` form of the reference's modified-attention test
+   * (tests/test_accuracy.py:176-194), read tile by tile inside the kernel. Dense K/V only. */
+  const void* score_bias;
+  int64_t bias_stride[3];
+  int32_t bias_pos;
 } LfPrefillArgs;
 
 typedef struct {
@@ -273,6 +282,15 @@ int lf_selftest_wait_timeout(int64_t limit_cycles, int32_t* status, int64_t* wai
  * [0, n_pages), is reported as LF_DEV_BAD_PAGE in `status` and that row is not written (the
  * kernel never stores outside the pools). Rows of different sequences must not share a page. */
 int lf_kv_append_bf16(const LfKvAppendArgs* args, void* stream);
+
+/* Elementwise out = a + b on bf16 [B, H, S, D] tensors (innermost stride 1, 16-byte aligned rows,
+ * D % 8 == 0), each with its own element strides of (b, h, s); `out` may alias `a` or `b`. One
+ * rounding to bf16, as the eager `Q + q_bias` and `scores @ V + out_bias` of the reference's
+ * modified-attention test (tests/test_accuracy.py:177-181) have; the compiled front end uses it
+ * for the query bias (before lf_prefill_bf16) and the output bias (after it). */
+int lf_add_bf16(const void* a, const void* b, void* out, int32_t B, int32_t H, int32_t S,
+                int32_t D, const int64_t* a_stride, const int64_t* b_stride,
+                const int64_t* out_stride, void* stream);
 
 #ifdef __cplusplus
 }

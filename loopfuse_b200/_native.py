@@ -17,7 +17,7 @@ EXPORTS = [
     "lf_decode_bf16", "lf_decode_paged_bf16", "lf_decode_auto_splits",
     "lf_decode_workspace_bytes", "lf_combine_f32", "lf_paged_gather_bf16",
     "lf_decode_bf16_static", "lf_prefill_kv_tile", "lf_tile_map_cache_stats",
-    "lf_kv_append_bf16", "lf_selftest_wait_timeout",
+    "lf_kv_append_bf16", "lf_selftest_wait_timeout", "lf_add_bf16",
 ]
 
 LF_STATIC_SCRATCH_BYTES = 8 << 20
@@ -37,6 +37,7 @@ class LfPrefillArgs(C.Structure):
         ("k_block_table", C.c_void_p), ("v_block_table", C.c_void_p), ("bt_stride", C.c_int64),
         ("page_size", C.c_int32), ("n_pages", C.c_int32),
         ("sm_margin", C.c_int32),
+        ("score_bias", C.c_void_p), ("bias_stride", C.c_int64 * 3), ("bias_pos", C.c_int32),
     ]
 
 
@@ -104,6 +105,10 @@ def load() -> C.CDLL:
     lib.lf_tile_map_cache_stats.restype = None
     lib.lf_kv_append_bf16.argtypes = [C.POINTER(LfKvAppendArgs), C.c_void_p]
     lib.lf_kv_append_bf16.restype = C.c_int
+    lib.lf_add_bf16.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+                                C.c_int32, C.c_int32, C.POINTER(C.c_int64),
+                                C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.c_void_p]
+    lib.lf_add_bf16.restype = C.c_int
     lib.lf_selftest_wait_timeout.argtypes = [C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.lf_selftest_wait_timeout.restype = C.c_int
     lib.lf_skip_range.argtypes = [C.c_int32] * 8 + [C.POINTER(C.c_int32), C.POINTER(C.c_int32)]

@@ -101,10 +101,16 @@ class CompiledAttention:
                 arg = evaluate_scalar(arg, self.placeholders, flat_args)
             mods.append(ScoreMod(m.op, arg))
         scale = 1.0
-        if mods and mods[0].op == MOD_MUL:   # the usual `* D ** -0.5`
+        bias_first = self.spec.score_bias is not None and self.spec.bias_pos == 0
+        if mods and mods[0].op == MOD_MUL and not bias_first:   # the usual `* D ** -0.5`
             scale = mods[0].arg
             mods = mods[1:]
         return scale, tuple(mods)
+
+    def _bias_pos(self, plan: "AttentionPlan") -> int:
+        """Position of the score bias in ``plan.mods`` (one less than in the captured chain when
+        its leading multiplier became the kernel's ``scale``)."""
+        return self.spec.bias_pos - (len(self.spec.mods) - len(plan.mods))
 
     def plan(self, flat_args: list) -> AttentionPlan:
         """The plan for this call's sizes; cached per (shapes, integer arguments)."""
@@ -155,6 +161,8 @@ class CompiledAttention:
         is_decode = (spec.mask_kind == MASK_NONE and decode_rows in _DECODE_GROUPS
                      and (Sq == 1 or group == 1) and (both_paged or not
                                                       (spec.k.paged or spec.v.paged)))
+        if spec.q_bias is not None or spec.out_bias is not None or spec.score_bias is not None:
+            is_decode = False   # the bias tensors are read by the prefill kernel only
         if is_decode:
             kernel = "paged_decode" if both_paged else "decode"
         else:
@@ -233,6 +241,20 @@ class CompiledAttention:
                 mods=plan.mods, mask_kind=spec.mask_kind, window=plan.window, status=status,
                 k_block_table=args[spec.k.block_table] if spec.k.paged else None,
                 v_block_table=args[spec.v.block_table] if spec.v.paged else None)
+        elif spec.q_bias is not None or spec.out_bias is not None or spec.score_bias is not None:
+            # Modified attention of the reference's tests (tests/test_accuracy.py:176-194): the
+            # query bias is added first (one bf16 rounding, as in the eager graph), the score
+            # bias is read inside the attention kernel, the output bias is added in place.
+            k, v = args[spec.k.placeholder], args[spec.v.placeholder]
+            if spec.q_bias is not None:
+                q = F.add_bf16(q, args[spec.q_bias])
+            out = F.prefill_attention(
+                q, k, v, scale=plan.scale, mods=plan.mods, mask_kind=spec.mask_kind,
+                window=plan.window, status=status,
+                score_bias=args[spec.score_bias] if spec.score_bias is not None else None,
+                bias_pos=self._bias_pos(plan))
+            if spec.out_bias is not None:
+                F.add_bf16(out, args[spec.out_bias], out=out)
         else:
             k, v = args[spec.k.placeholder], args[spec.v.placeholder]
             out = torch.empty((plan.B, plan.Hq, plan.Sq, plan.D), dtype=q.dtype, device=q.device)

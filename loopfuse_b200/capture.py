@@ -7,6 +7,9 @@ graphs directly, walking back from the graph output:
     out   = view(bmm(view(expand(P)), view(expand(V'))))
     P     = _softmax(M, -1, False)
     M     = [causal_mask | sliding_mask]* ( score-mod chain ( view(bmm(Q', K'^T)) ) )
+    optionally with the additive tensors of the reference's modified attention
+    (tests/test_accuracy.py:176-194): out + out_bias, (Q + q_bias), and one `+ scores_bias`
+    ([B,H,S,S]) anywhere in the score-mod chain
     K',V' = dense input, optionally through repeat_interleave (unsqueeze -> expand -> clone -> view)
             or a paged gather  paged_load(pool, table) [-> view merging page dims] -> transpose(1, 2)
 
@@ -81,6 +84,11 @@ class _Matcher:
                 node.meta.get("val"), torch.Tensor):
             return self.ph_index[node]
         raise NotImplementedError(f"{what}: expected a graph input, found {_describe(node)}")
+
+    def _is_tensor_input(self, node: Any, rank: int) -> bool:
+        return (isinstance(node, fx.Node) and node.op == "placeholder"
+                and isinstance(node.meta.get("val"), torch.Tensor)
+                and node.meta["val"].dim() == rank)
 
     def _strip_bmm_operand(self, node: fx.Node) -> fx.Node:
         """Undo the batch flattening around bmm: [expand ->] [clone ->] view(3-D)."""
@@ -159,6 +167,13 @@ class _Matcher:
         if not isinstance(outs, (tuple, list)) or len(outs) != 1:
             raise NotImplementedError("expected a graph with exactly one output")
         node = outs[0]
+        out_bias = None
+        if _is(node, aten.add.Tensor):
+            a, b = node.args[0], node.args[1]
+            if _is(b, *_VIEW_LIKE) and not _is(a, *_VIEW_LIKE):
+                a, b = b, a
+            out_bias = self._tensor_placeholder(b, "output bias")
+            node = a
         if not _is(node, *_VIEW_LIKE) or not _is(node.args[0], aten.bmm.default):
             raise NotImplementedError(
                 f"graph output is not `probabilities @ V`: {_describe(node)}")
@@ -197,6 +212,8 @@ class _Matcher:
 
         # score-mod chain, collected back to front
         mods: list[ScoreMod] = []
+        score_bias = None
+        ops_after_bias = 0
         while not (_is(node, *_VIEW_LIKE) and _is(node.args[0], aten.bmm.default)):
             if _is(node, *_CASTS):
                 # dtype round trips of the eager bf16 graph; the kernels keep scores in fp32
@@ -213,6 +230,19 @@ class _Matcher:
                     raise NotImplementedError("pow is only supported with exponent 2")
                 mods.append(ScoreMod(MOD_SQUARE))
                 node = node.args[0]
+            elif _is(node, aten.add.Tensor) and any(self._is_tensor_input(x, 4)
+                                                    for x in node.args[:2]):
+                # + scores_bias: a full [B, H, Sq, Skv] graph input
+                a, b = node.args[0], node.args[1]
+                if self._is_tensor_input(a, 4):
+                    a, b = b, a
+                if score_bias is not None:
+                    raise NotImplementedError("only one additive score tensor is supported")
+                if len(node.args) > 2 or node.kwargs.get("alpha", 1) != 1:
+                    raise NotImplementedError("add with alpha is not supported")
+                score_bias = self.ph_index[b]
+                ops_after_bias = len(mods)
+                node = a
             elif _is(node, aten.mul.Tensor, aten.add.Tensor):
                 a, b = node.args[0], node.args[1]
                 tensor_side, scalar_side = (a, b)
@@ -242,6 +272,11 @@ class _Matcher:
 
         qk = node.args[0]
         q_node = self._strip_bmm_operand(qk.args[0])
+        q_bias = None
+        if _is(q_node, aten.add.Tensor):
+            a, b = q_node.args[0], q_node.args[1]
+            q_bias = self._tensor_placeholder(b, "query bias")
+            q_node = a
         kt_node = self._strip_bmm_operand(qk.args[1])
         if not _is_transpose(kt_node, 2, 3):
             raise NotImplementedError(
@@ -256,8 +291,16 @@ class _Matcher:
             if dt != torch.bfloat16:
                 raise NotImplementedError(
                     f"{what} has dtype {dt}; the sm_100a kernels take bfloat16 inputs")
+        biases = [i for i in (q_bias, out_bias, score_bias) if i is not None]
+        for idx in biases:
+            if self.placeholders[idx].meta["val"].dtype != torch.bfloat16:
+                raise NotImplementedError("bias tensors must be bfloat16")
+        if biases and (k_src.paged or v_src.paged or k_src.repeated):
+            raise NotImplementedError("bias tensors are supported with dense, ungrouped K/V only")
         return AttentionSpec(q=q_idx, k=k_src, v=v_src, mods=tuple(mods), mask_kind=mask_kind,
-                             windows=tuple(windows), n_args=len(self.placeholders))
+                             windows=tuple(windows), n_args=len(self.placeholders),
+                             q_bias=q_bias, out_bias=out_bias, score_bias=score_bias,
+                             bias_pos=len(mods) - ops_after_bias)
 
 
 def _describe(node: Any) -> str:

@@ -76,6 +76,31 @@ constexpr int kModeGeneric = 2;  // logit2 = mods(raw * a) * c2
 constexpr int kModeBounded = 3;
 constexpr float kBoundedMaxC2 = 80.f;
 
+// Division by a divisor fixed at launch time: q = (mulhi(n, mul) + n) >> shift (Granlund &
+// Montgomery's round-up method; exact for every 0 <= n < 2^31). The item decode of the
+// persistent kernels runs on one warp that gets few issue slots; real divisions (a few dozen
+// dependent instructions each) made it take thousands of clocks.
+struct FastDiv {
+  uint32_t mul, shift, d;
+  static FastDiv make(int32_t divisor) {
+    FastDiv f;
+    f.d = static_cast<uint32_t>(divisor);
+    f.shift = 0;
+    while ((1u << f.shift) < f.d) ++f.shift;
+    f.mul = static_cast<uint32_t>(((static_cast<uint64_t>(1) << 32) *
+                                   ((static_cast<uint64_t>(1) << f.shift) - f.d)) / f.d + 1);
+    return f;
+  }
+  __host__ __device__ __forceinline__ uint32_t div(uint32_t n) const {
+#ifdef __CUDA_ARCH__
+    const uint32_t hi = __umulhi(n, mul);
+#else
+    const uint32_t hi = static_cast<uint32_t>((static_cast<uint64_t>(n) * mul) >> 32);
+#endif
+    return static_cast<uint32_t>((static_cast<uint64_t>(hi) + n) >> shift);
+  }
+};
+
 struct PrefillParams {
   __nv_bfloat16* out;
   int64_t o_stride[3];
@@ -87,10 +112,16 @@ struct PrefillParams {
   float qc[4];       // bounded mode: tanh polynomial in raw^2, scaled to give logit2 / raw
   float ylim[2];     // bounded mode: validity limits of the two polynomials, on raw^2
   ModChain mods;
+  const __nv_bfloat16* bias;  // additive score bias [B, Hq, Sq, Skv] (generic mode only) or null
+  int64_t bias_stride[3];
+  int32_t bias_pos;           // the bias is added after this many ops of `mods`
   int32_t* status;
   int32_t* dbg_ranges;
   // Persistent (bounded-mode) kernel only: the work queue.
   int32_t n_pairs;       // query-tile pairs per head
+  int32_t n_deferred;    // persistent kernels: lightest pairs of a head kept for the queue's end
+  int32_t main_items;    // (n_pairs - n_deferred) * Hq * B: items ahead of the deferred ones
+  FastDiv div_main, div_deferred, div_hq, div_group;  // divisors of the item decode
   int32_t n_items;       // n_pairs * Hq * B
   unsigned int* ticket;  // device counter, zero at launch
   int32_t sm_margin;     // SMs left without a CTA
@@ -513,11 +544,45 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         const bool masked = rel_lo > 0 || rel_hi < kTileK - 1;
 
         if constexpr (MODE == kModeGeneric) {
+          if (p.bias == nullptr) {
 #pragma unroll
-          for (int c = 0; c < 2; ++c)
+            for (int c = 0; c < 2; ++c)
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              sr[c][i] = __float_as_uint(apply_mods(p.mods, __uint_as_float(sr[c][i]) * p.a));
+              for (int i = 0; i < 32; ++i)
+                sr[c][i] = __float_as_uint(apply_mods(p.mods, __uint_as_float(sr[c][i]) * p.a));
+          } else {
+            // This row's 64 bias values of the block: 128 contiguous bytes, eight 16-byte loads
+            // (rows past Sq read the last row, columns past Skv are not read: both are masked
+            // or clipped later).
+            const __nv_bfloat16* brow = p.bias + b * p.bias_stride[0] + h * p.bias_stride[1] +
+                                        static_cast<int64_t>(min(grow, p.Sq - 1)) * p.bias_stride[2] +
+                                        c0;
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+#pragma unroll
+              for (int i8 = 0; i8 < 4; ++i8) {
+                const int cc = c * 32 + i8 * 8;
+                uint32_t w[4] = {0u, 0u, 0u, 0u};
+                if (c0 + cc + 8 <= p.Skv) {
+                  const uint4 v4 = ldg_stream_16(brow + cc);
+                  w[0] = v4.x; w[1] = v4.y; w[2] = v4.z; w[3] = v4.w;
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 8; ++e)
+                    if (c0 + cc + e < p.Skv)
+                      w[e >> 1] |= static_cast<uint32_t>(__bfloat16_as_ushort(brow[cc + e]))
+                                   << ((e & 1) * 16);
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const float bv = __uint_as_float((e & 1) ? (w[e >> 1] & 0xffff0000u)
+                                                           : (w[e >> 1] << 16));
+                  float sv = __uint_as_float(sr[c][i8 * 8 + e]) * p.a;
+                  sv = apply_mods_range(p.mods, sv, 0, p.bias_pos) + bv;
+                  sr[c][i8 * 8 + e] = __float_as_uint(apply_mods_range(p.mods, sv, p.bias_pos, LF_MAX_MODS));
+                }
+              }
+          }
         }
 
         // Pass 1: row max (and min, for the softcap range check), independent chains.
@@ -964,6 +1029,12 @@ static int launch_prefill_bounded(const CUtensorMap& mq, const CUtensorMap& mk,
     configured_dev = dev;
   }
   p.n_pairs = (p.n_qtiles + 1) / 2;
+  p.n_deferred = (p.mask_kind == LF_MASK_CAUSAL && p.Sq == p.Skv) ? p.n_pairs / 4 : 0;
+  p.main_items = static_cast<int32_t>(static_cast<int64_t>(p.n_pairs - p.n_deferred) * p.Hq * B);
+  p.div_main = FastDiv::make(p.n_pairs - p.n_deferred);
+  p.div_deferred = FastDiv::make(p.n_deferred > 0 ? p.n_deferred : 1);
+  p.div_hq = FastDiv::make(p.Hq);
+  p.div_group = FastDiv::make(p.group);
   const int64_t n_items = static_cast<int64_t>(p.n_pairs) * p.Hq * B;
   if (n_items > 0x7fffffff - 4096) return LF_ERR_TOO_LARGE;
   p.n_items = static_cast<int32_t>(n_items);
@@ -1006,6 +1077,12 @@ static int launch_prefill_wide(const CUtensorMap& mq, const CUtensorMap& mk,
     configured_dev = dev;
   }
   p.n_pairs = (p.n_qtiles + 1) / 2;
+  p.n_deferred = (p.mask_kind == LF_MASK_CAUSAL && p.Sq == p.Skv) ? p.n_pairs / 4 : 0;
+  p.main_items = static_cast<int32_t>(static_cast<int64_t>(p.n_pairs - p.n_deferred) * p.Hq * B);
+  p.div_main = FastDiv::make(p.n_pairs - p.n_deferred);
+  p.div_deferred = FastDiv::make(p.n_deferred > 0 ? p.n_deferred : 1);
+  p.div_hq = FastDiv::make(p.Hq);
+  p.div_group = FastDiv::make(p.group);
   const int64_t n_items = static_cast<int64_t>(p.n_pairs) * p.Hq * B;
   if (n_items > 0x7fffffff - 4096) return LF_ERR_TOO_LARGE;
   p.n_items = static_cast<int32_t>(n_items);
@@ -1065,6 +1142,9 @@ static int prefill_impl(const LfPrefillArgs* a, void* const* launch) {
   for (int i = 0; i < 4; ++i) p.qc[i] = 0.f;
   p.ylim[0] = p.ylim[1] = 0.f;
   p.n_pairs = 0;
+  p.n_deferred = 0;
+  p.main_items = 0;
+  p.div_main = p.div_deferred = p.div_hq = p.div_group = FastDiv::make(1);
   p.n_items = 0;
   p.ticket = nullptr;
   if (a->sm_margin < 0) return LF_ERR_INVALID_ARG;
@@ -1098,11 +1178,21 @@ static int prefill_impl(const LfPrefillArgs* a, void* const* launch) {
     p.mods.op[i] = 0;
     p.mods.arg[i] = 0.f;
   }
+  p.bias = static_cast<const __nv_bfloat16*>(a->score_bias);
+  p.bias_pos = a->bias_pos;
+  for (int i = 0; i < 3; ++i) p.bias_stride[i] = a->bias_stride[i];
+  if (p.bias) {
+    if (p.paged) return LF_ERR_UNSUPPORTED;
+    if (a->bias_pos < 0 || a->bias_pos > a->n_mod) return LF_ERR_INVALID_ARG;
+    if (reinterpret_cast<uintptr_t>(a->score_bias) & 15u) return LF_ERR_ALIGNMENT;
+    for (int i = 0; i < 3; ++i)
+      if (a->bias_stride[i] % 8) return LF_ERR_ALIGNMENT;
+  }
 
   // Pick the score-function mode. Leading and trailing constant multipliers are folded into
   // `a` (before) and `c2` (after); c2 must stay positive for the max-before-scale shortcut.
   int mode = kModeGeneric;
-  {
+  if (!p.bias) {  // (a score bias always takes the generic path: the chain is split around it)
     int i = 0;
     float pre = a->scale;
     while (i < a->n_mod && (a->mod_op[i] == LF_MOD_MUL || a->mod_op[i] == LF_MOD_DIV)) {
@@ -1140,6 +1230,8 @@ static int prefill_impl(const LfPrefillArgs* a, void* const* launch) {
         p.ylim[1] = kTanhPoly3Limit * kTanhPoly3Limit / a2;
       }
     }
+  }
+  {
     if (mode == kModeGeneric) {
       p.a = a->scale;
       p.c2 = kLog2eF;

@@ -72,11 +72,22 @@ __device__ __forceinline__ ItemGeom decode_item(const PrefillParams& p, int it,
                                                 int tile_k = kTileK) {
   ItemGeom g;
   g.it = it;
-  const int pair = p.n_pairs - 1 - it % p.n_pairs;  // heaviest query tiles of a head first
-  const int hb = it / p.n_pairs;
-  g.h = hb % p.Hq;
-  g.b = hb / p.Hq;
-  g.hkv = g.h / p.group;
+  // Heaviest query tiles of a head first. With a causal mask the lightest quarter of the pairs
+  // of every head (n_deferred per head) is kept for the end of the queue: the last items that
+  // the CTAs pick up are then short, so they finish close together (those pairs read only the
+  // first few K/V blocks of their head again, which costs next to nothing).
+  int pair, hb;
+  if (it < p.main_items) {
+    hb = static_cast<int>(p.div_main.div(it));
+    pair = p.n_pairs - 1 - (it - hb * static_cast<int>(p.div_main.d));
+  } else {
+    const int r = it - p.main_items;
+    hb = static_cast<int>(p.div_deferred.div(r));
+    pair = p.n_deferred - 1 - (r - hb * p.n_deferred);
+  }
+  g.b = static_cast<int>(p.div_hq.div(hb));
+  g.h = hb - g.b * p.Hq;
+  g.hkv = static_cast<int>(p.div_group.div(g.h));
   g.iq0 = pair * 2;
   skip_range(p.mask_kind, p.window, p.causal_offset, p.Sq, p.Skv, kTileQ, tile_k, g.iq0, &g.lo0,
              &g.hi0);

@@ -76,8 +76,14 @@ def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scal
                       kv_tile: int = 0, sm_margin: int = 0,
                       k_block_table: Optional[torch.Tensor] = None,
                       v_block_table: Optional[torch.Tensor] = None,
-                      seq_len: Optional[int] = None) -> torch.Tensor:
+                      seq_len: Optional[int] = None,
+                      score_bias: Optional[torch.Tensor] = None,
+                      bias_pos: Optional[int] = None) -> torch.Tensor:
     """softmax(mask(mods(scale * q k^T))) v for q [B,Hq,Sq,D], k/v [B,Hkv,Skv,D] (bf16).
+
+    ``score_bias`` (bf16 ``[B, Hq, Sq, Skv]``) is added to the scores after the first
+    ``bias_pos`` ops of ``mods`` (default: after all of them) and before the mask; the kernel
+    reads it tile by tile (dense k / v only).
 
     With ``k_block_table`` (``v_block_table``), ``k`` (``v``) is a paged pool
     ``[pages, page_size, Hkv, D]`` (or ``[pages, Hkv, D]``, one token per page) read through that
@@ -90,9 +96,44 @@ def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scal
     a, out, dev = _prefill_args(q, k, v, scale, mods, mask_kind, window, causal_offset, out,
                                 status, dbg_ranges, kv_tile, sm_margin, k_block_table,
                                 v_block_table, seq_len)
+    if score_bias is not None:
+        _require_cuda(score_bias)
+        _check_bf16_lastdim(score_bias, "score_bias")
+        if tuple(score_bias.shape) != (a.B, a.Hq, a.Sq, a.Skv):
+            raise ValueError(f"score_bias must be [B, Hq, Sq, Skv] = "
+                             f"{(a.B, a.Hq, a.Sq, a.Skv)}, got {tuple(score_bias.shape)}")
+        a.score_bias = score_bias.data_ptr()
+        for i in range(3):
+            a.bias_stride[i] = score_bias.stride(i)
+        a.bias_pos = a.n_mod if bias_pos is None else int(bias_pos)
     with torch.cuda.device(dev):
         rc = _native.load().lf_prefill_bf16(C.byref(a), _stream_ptr(dev))
     _native.check(rc, "lf_prefill_bf16")
+    return out
+
+
+def add_bf16(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = a + b for bf16 [B, H, S, D] tensors of one shape (any strides with innermost 1);
+    ``out`` may be ``a`` or ``b``. The query-bias and output-bias steps of a biased attention."""
+    dev = _require_cuda(a, b)
+    for t, n in ((a, "a"), (b, "b")):
+        _check_bf16_lastdim(t, n)
+    if a.dim() != 4 or a.shape != b.shape:
+        raise ValueError(f"add_bf16 takes two 4-D tensors of one shape, got {tuple(a.shape)} "
+                         f"and {tuple(b.shape)}")
+    if out is None:
+        out = torch.empty(a.shape, dtype=torch.bfloat16, device=dev)
+    else:
+        _require_cuda(out)
+        _check_bf16_lastdim(out, "out")
+        if out.shape != a.shape:
+            raise ValueError("out must have the operands' shape")
+    B, H, S, D = a.shape
+    strides = [(C.c_int64 * 3)(*[t.stride(i) for i in range(3)]) for t in (a, b, out)]
+    with torch.cuda.device(dev):
+        rc = _native.load().lf_add_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), B, H, S, D,
+                                        strides[0], strides[1], strides[2], _stream_ptr(dev))
+    _native.check(rc, "lf_add_bf16")
     return out
 
 

@@ -78,6 +78,11 @@ class AttentionSpec:
     mask_kind: int = MASK_NONE
     windows: tuple = ()       # window of every sliding_mask met (int or ScalarExpr); min applies
     n_args: int = 0           # number of flat arguments of the compiled callable
+    # Additive tensors of the reference's modified attention (tests/test_accuracy.py:176-194):
+    q_bias: Optional[int] = None      # flat argument index of a [B,Hq,Sq,D] tensor added to Q
+    out_bias: Optional[int] = None    # ... added to the output
+    score_bias: Optional[int] = None  # ... of a [B,Hq,Sq,Skv] tensor added to the scores
+    bias_pos: int = 0                 # the score bias is added after this many ops of ``mods``
 
     @property
     def window(self) -> int:
@@ -89,8 +94,13 @@ class AttentionSpec:
     def describe(self) -> str:
         mask = {MASK_NONE: "none", MASK_CAUSAL: "causal",
                 MASK_CAUSAL_WINDOW: f"causal_window({list(self.windows)})"}[self.mask_kind]
+        bias = "".join(f", {n}=arg{i}" for n, i in (("q_bias", self.q_bias),
+                                                    ("score_bias", self.score_bias),
+                                                    ("out_bias", self.out_bias)) if i is not None)
+        if self.score_bias is not None:
+            bias += f"@{self.bias_pos}"
         return (f"AttentionSpec(q=arg{self.q}, k={self.k}, v={self.v}, "
-                f"mods={list(self.mods)}, mask={mask})")
+                f"mods={list(self.mods)}, mask={mask}{bias})")
 
 
 def skip_range(mask_kind: int, window: int, causal_offset: int, s_q: int, s_kv: int,

@@ -16,6 +16,8 @@ What each function follows (paths inside tomatillos/loopfuse):
   paged_load_ref      loopfuse/torch_backend/__init__.py:46-56
   attention_ref       the user-level functions of tests/benchmark.py:79-83, 142-147, 221-230,
                       328-334, 481-484 and tests/test_accuracy.py:131-135
+  modified_attention_ref   the function of tests/test_accuracy.py:176-181 (query, score and output
+                      bias), with the two bf16 roundings its eager graph has around the matmuls
   kv_append_ref       the inverse of paged_load_ref: the cache / table convention of
                       tests/benchmark.py:308-319 read by loopfuse/torch_backend/__init__.py:46-56,
                       used as an indexed store (pool[block_table[b, t // P], t % P] = new row)
@@ -168,6 +170,26 @@ def attention_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: O
             raise ValueError(mask)
         outs.append(torch.softmax(s, dim=-1) @ vb)
     return torch.cat(outs)
+
+
+def modified_attention_ref(q, k, v, q_bias, scores_bias, out_bias, *, mult: float = 3.5,
+                           batch_chunk: int = 1) -> torch.Tensor:
+    """softmax(causal((Q + q_bias) K^T * D^-0.5 * mult + scores_bias)) V + out_bias.
+
+    The eager bf16 graph rounds `Q + q_bias` to bf16 before the matmul and adds `out_bias` to the
+    bf16 attention output; both roundings are kept here (they are part of what the function
+    computes on bf16 tensors), everything between them is fp32."""
+    qb = (q.float().cpu() + q_bias.float().cpu()).to(torch.bfloat16).float()
+    k, v = k.float().cpu(), v.float().cpu()
+    sb = scores_bias.float().cpu()
+    scale = q.shape[-1] ** -0.5
+    outs = []
+    for b0 in range(0, q.shape[0], batch_chunk):
+        s = qb[b0:b0 + batch_chunk] @ k[b0:b0 + batch_chunk].transpose(-2, -1) * scale
+        s = causal_mask_general(s * mult + sb[b0:b0 + batch_chunk])
+        outs.append(torch.softmax(s, dim=-1) @ v[b0:b0 + batch_chunk])
+    att = torch.cat(outs).to(torch.bfloat16).float()
+    return att + out_bias.float().cpu()
 
 
 def softcap_mods(c: float) -> list:

@@ -145,6 +145,29 @@ def test_generic_score_mods_are_captured_in_order():
     assert mod_names(plan) == [("mul", 3.5), ("add", 1.0), ("relu", 0.0), ("add", -2.0)]
 
 
+def test_modified_attention_of_the_reference_tests_is_captured():
+    """The graph of the reference's tests/test_accuracy.py:176-181: query bias, score multiplier
+    and score bias, causal mask, output bias."""
+    def fn(Q, K, V, q_bias, scores_bias, out_bias):
+        QK = (Q + q_bias) @ K.transpose(-2, -1) * (Q.shape[-1] ** -0.5)
+        QK = QK * 3.5 + scores_bias
+        masked = torch.ops.loopfuse.causal_mask(QK)
+        return torch.softmax(masked, dim=-1) @ V + out_bias
+
+    q = torch.randn(2, 2, 128, 64, dtype=torch.bfloat16)
+    sb = torch.randn(2, 2, 128, 128, dtype=torch.bfloat16)
+    plan = compile_plan(fn, (q, q.clone(), q.clone(), q.clone(), sb, q.clone()))
+    spec = plan.spec
+    assert plan.kernel == "prefill" and plan.mask_kind == 1
+    # (flat argument indices: symbolic sizes sit between the tensors)
+    idx = (spec.q, spec.k.placeholder, spec.v.placeholder, spec.q_bias, spec.score_bias,
+           spec.out_bias)
+    assert None not in idx and len(set(idx)) == 6
+    assert plan.scale == pytest.approx(0.125)
+    assert mod_names(plan) == [("mul", 3.5)]
+    assert spec.bias_pos == 2          # after `* D ** -0.5` and `* 3.5` of the captured chain
+
+
 def test_mode_kwarg_is_accepted():
     w = small("causal_tiny")
     plan = compile_plan(w.fn(), make_inputs(w), mode=None)
@@ -161,8 +184,8 @@ def test_import_aliases_of_the_reference_paths():
 def test_unsupported_graphs_raise(case):
     from torch._dynamo.exc import BackendCompilerFailed
     q = torch.randn(1, 2, 64, 64, dtype=torch.bfloat16)
-    if case == "bias_tensor":
-        bias = torch.randn(1, 2, 64, 64, dtype=torch.bfloat16)
+    if case == "bias_tensor":   # a broadcast bias (only a full [B, H, S, S] one is supported)
+        bias = torch.randn(64, 64, dtype=torch.bfloat16)
 
         def fn(q, k, v):
             return torch.softmax(q @ k.transpose(-2, -1) + bias, dim=-1) @ v

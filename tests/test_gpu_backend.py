@@ -108,6 +108,58 @@ def test_reference_style_paged_prefill_gqa():
     assert (out.float().cpu() - want).abs().max().item() <= TOL
 
 
+@pytest.mark.parametrize("S_", [1024, 200])
+def test_reference_style_modified_attention(S_):
+    # tests/test_accuracy.py:172-194: B4 H8 S1024 D64 with a query bias, a score multiplier and
+    # a full [B, H, S, S] score bias, causal mask, output bias (S = 200: ragged tiles)
+    def fn(Q, K, V, q_bias, scores_bias, out_bias):
+        QK = (Q + q_bias) @ K.transpose(-2, -1) * (Q.shape[-1] ** -0.5)
+        QK = QK * 3.5 + scores_bias
+        masked_attn = torch.ops.loopfuse.causal_mask(QK)
+        scores = torch.softmax(masked_attn, dim=-1)
+        return scores @ V + out_bias
+
+    g = torch.Generator().manual_seed(8)
+    B, H, D = 4, 8, 64
+    mk = lambda *shape: torch.randn(*shape, generator=g).bfloat16()
+    Q, K, V, qb, ob = (mk(B, H, S_, D) for _ in range(5))
+    sb = mk(B, H, S_, S_)
+    out = compile_and_run(fn, (Q, K, V, qb, sb, ob))
+    want = O.modified_attention_ref(Q, K, V, qb, sb, ob, batch_chunk=B)
+    # 2e-2 on the attention part, plus one bf16 step of the biased output (its last rounding
+    # can fall the other way when the attention part differs within its tolerance)
+    torch.testing.assert_close(out.float().cpu(), want, atol=2e-2, rtol=2 ** -7)
+
+
+def test_score_bias_position_in_the_chain():
+    """C-ABI level: the bias is added after `bias_pos` ops of the chain (here between a tanh and
+    a multiplier), not at its end."""
+    from loopfuse_b200 import functional as F, spec as SP
+    g = torch.Generator().manual_seed(9)
+    B, H, S_, D = 1, 2, 192, 128
+    mk = lambda *shape: torch.randn(*shape, generator=g).bfloat16()
+    q, k, v = (mk(B, H, S_, D) for _ in range(3))
+    sb = mk(B, H, S_, S_)
+    mods = [SP.ScoreMod(SP.MOD_TANH), SP.ScoreMod(SP.MOD_MUL, 2.0)]
+    out = F.prefill_attention(q.cuda(), k.cuda(), v.cuda(), scale=D ** -0.5, mods=mods,
+                              mask_kind=SP.MASK_CAUSAL, score_bias=sb.cuda(), bias_pos=1)
+    s = torch.tanh(q.float() @ k.float().transpose(-2, -1) * D ** -0.5) + sb.float()
+    s = O.causal_mask_general(s * 2.0)
+    want = torch.softmax(s, dim=-1) @ v.float()
+    assert (out.float().cpu() - want).abs().max().item() <= TOL
+
+
+def test_add_bf16_is_bit_exact():
+    from loopfuse_b200 import functional as F
+    g = torch.Generator().manual_seed(10)
+    a = torch.randn(2, 3, 70, 128, generator=g).bfloat16().cuda()
+    b = torch.randn(2, 70, 3, 128, generator=g).bfloat16().cuda().transpose(1, 2)   # strided
+    assert torch.equal(F.add_bf16(a, b), a + b)
+    c = a.clone()
+    F.add_bf16(c, b, out=c)
+    assert torch.equal(c, a + b)
+
+
 def test_status_word_is_checked_when_asked(monkeypatch):
     """LF_CHECK_STATUS=1: an out-of-range block-table entry raises through the compiled
     function (the reference's eager gather would raise an index error); the kernel itself
