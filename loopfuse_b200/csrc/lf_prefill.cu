@@ -118,6 +118,7 @@ struct PrefillParams {
   int32_t* status;
   int32_t* dbg_ranges;
   // Persistent (bounded-mode) kernel only: the work queue.
+  int32_t single;        // running-max kernel: one query tile per CTA instead of a pair
   int32_t n_pairs;       // query-tile pairs per head
   int32_t n_deferred;    // persistent kernels: lightest pairs of a head kept for the queue's end
   int32_t main_items;    // (n_pairs - n_deferred) * Hq * B: items ahead of the deferred ones
@@ -188,14 +189,17 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
   const int h = blockIdx.y;
   const int b = blockIdx.z;
   const int hkv = h / p.group;
-  const int iq0 = pair * 2;
+  // (`single`: one query tile per CTA; the second tile slot stays empty. Chosen by the host for
+  // problems whose pairs would not fill the SMs: twice the CTAs, each with the tensor pipe and
+  // the issue slots of an SM to itself, halve the time of a launch that is a single wave.)
+  const int iq0 = p.single ? pair : pair * 2;
 
   int lo_t[2], hi_t[2];
   skip_range(p.mask_kind, p.window, p.causal_offset, p.Sq, p.Skv, kTileQ, kTileK, iq0, &lo_t[0],
              &hi_t[0]);
   skip_range(p.mask_kind, p.window, p.causal_offset, p.Sq, p.Skv, kTileQ, kTileK, iq0 + 1,
              &lo_t[1], &hi_t[1]);
-  const bool tile_valid[2] = {iq0 * kTileQ < p.Sq, (iq0 + 1) * kTileQ < p.Sq};
+  const bool tile_valid[2] = {iq0 * kTileQ < p.Sq, !p.single && (iq0 + 1) * kTileQ < p.Sq};
   const bool has_work[2] = {tile_valid[0] && hi_t[0] > lo_t[0], tile_valid[1] && hi_t[1] > lo_t[1]};
   int lo = 0, hi = 0;
   if (has_work[0] && has_work[1]) {
@@ -990,8 +994,12 @@ static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CU
     configured_dev = dev;
   }
   const int pairs = (p.n_qtiles + 1) / 2;
-  dim3 grid(pairs, p.Hq, B);
-  prefill_kernel<D, MODE><<<grid, kPrefillThreads, smem, st>>>(mq, mk, mv, p);
+  static thread_local int sm_count = 0;
+  if (sm_count == 0) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  PrefillParams pp = p;
+  pp.single = (p.n_qtiles > 1 && static_cast<int64_t>(pairs) * p.Hq * B < sm_count) ? 1 : 0;
+  dim3 grid(pp.single ? p.n_qtiles : pairs, p.Hq, B);
+  prefill_kernel<D, MODE><<<grid, kPrefillThreads, smem, st>>>(mq, mk, mv, pp);
   return check_launch("prefill_kernel");
 }
 
@@ -1141,6 +1149,7 @@ static int prefill_impl(const LfPrefillArgs* a, void* const* launch) {
   p.dbg_ranges = a->dbg_ranges;
   for (int i = 0; i < 4; ++i) p.qc[i] = 0.f;
   p.ylim[0] = p.ylim[1] = 0.f;
+  p.single = 0;
   p.n_pairs = 0;
   p.n_deferred = 0;
   p.main_items = 0;
