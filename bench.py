@@ -334,8 +334,8 @@ def copy_ceiling(dev, nbytes: int = 256 << 20) -> dict:
     d_in = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     d_out = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     s1, s2 = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    best = [0.0, 0.0]
-    for _ in range(3):
+    seen: list = [[], []]
+    for _ in range(5):
         torch.cuda.synchronize()
         a1, b1 = events()
         a2, b2 = events()
@@ -348,8 +348,11 @@ def copy_ceiling(dev, nbytes: int = 256 << 20) -> dict:
             h_out.copy_(d_out, non_blocking=True)
             b2.record()
         torch.cuda.synchronize()
-        best[0] = max(best[0], nbytes / 1e9 / (a1.elapsed_time(b1) * 1e-3))
-        best[1] = max(best[1], nbytes / 1e9 / (a2.elapsed_time(b2) * 1e-3))
+        seen[0].append(nbytes / 1e9 / (a1.elapsed_time(b1) * 1e-3))
+        seen[1].append(nbytes / 1e9 / (a2.elapsed_time(b2) * 1e-3))
+    # the median of five: other tenants of the host's memory and PCIe switches come and go, and
+    # the best of a few tries would describe a quieter machine than the end-to-end loop sees
+    best = [sorted(x)[len(x) // 2] for x in seen]
     return {"h2d_gbs": best[0], "d2h_gbs": best[1]}
 
 
