@@ -154,30 +154,6 @@ __device__ __forceinline__ float apply_mods(const ModChain& mc, float s) {
   return s;
 }
 
-// Ops [lo, hi) of the chain.
-__device__ __forceinline__ float apply_mods_range(const ModChain& mc, float s, int lo, int hi) {
-#pragma unroll
-  for (int i = 0; i < LF_MAX_MODS; ++i) {
-    if (i >= lo && i < hi && i < mc.n) {
-      const float a = mc.arg[i];
-      switch (mc.op[i]) {
-        case LF_MOD_MUL: s *= a; break;
-        case LF_MOD_ADD: s += a; break;
-        case LF_MOD_TANH: s = tanhf(s); break;
-        case LF_MOD_EXP: s = __expf(s); break;
-        case LF_MOD_EXP2: s = exp2f(s); break;
-        case LF_MOD_SIN: s = sinf(s); break;
-        case LF_MOD_COS: s = cosf(s); break;
-        case LF_MOD_RELU: s = fmaxf(s, 0.f); break;
-        case LF_MOD_SQUARE: s = s * s; break;
-        case LF_MOD_DIV: s = s / a; break;
-        default: break;
-      }
-    }
-  }
-  return s;
-}
-
 // One lane of the (converged) warp is elected; the others get false. A role whose work is issued
 // by a single lane (tcgen05.mma, TMA) should still run its loop with the whole warp converged
 // and guard only the issuing instructions with this predicate: a warp that has diverged into a

@@ -367,14 +367,20 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     publish_up_to(n);
   } else if (warp == kProducerWarp) {
     // ---------------- TMA producer ----------------
-    if (lane == 0) {
+    // The whole warp runs the loop and waits; the elected lane issues the copies (a warp that
+    // has diverged into a single-lane branch gets few issue slots next to the softmax warps).
+    {
+      const bool elected = elect_one_sync();
       for (int t = 0; t < 2; ++t) {
         if (!has_work[t]) continue;
-        mbar_arrive_expect_tx(&bars->q_full[t], kQTileBytes);
+        if (elected) {
+          mbar_arrive_expect_tx(&bars->q_full[t], kQTileBytes);
 #pragma unroll
-        for (int kb = 0; kb < kBlocksD; ++kb)
-          tma_load_4d(sQ + t * kQTileBytes + kb * kQBlockBytes, &tmap_q, &bars->q_full[t],
-                      kb * 64, (iq0 + t) * kTileQ, h, b);
+          for (int kb = 0; kb < kBlocksD; ++kb)
+            tma_load_4d(sQ + t * kQTileBytes + kb * kQBlockBytes, &tmap_q, &bars->q_full[t],
+                        kb * 64, (iq0 + t) * kTileQ, h, b);
+        }
+        __syncwarp();
       }
       int n = 0;
       bool ok = true;
@@ -391,18 +397,22 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
           ok = false;
           return;
         }
-        mbar_arrive_expect_tx(&bars->kv_full[stage], jb >= 0 ? 2 * kKVTileBytes : kKVTileBytes);
-        unsigned char* dst = sKV + stage * (2 * kKVTileBytes);
-#pragma unroll
-        for (int kb = 0; kb < kBlocksD; ++kb)
-          tma_load_4d(dst + kb * kKVBlockBytes, tma, &bars->kv_full[stage], kb * 64, ja * kTileK,
-                      hkv, b);
-        if (jb >= 0) {
+        if (elected) {
+          mbar_arrive_expect_tx(&bars->kv_full[stage],
+                                jb >= 0 ? 2 * kKVTileBytes : kKVTileBytes);
+          unsigned char* dst = sKV + stage * (2 * kKVTileBytes);
 #pragma unroll
           for (int kb = 0; kb < kBlocksD; ++kb)
-            tma_load_4d(dst + kKVTileBytes + kb * kKVBlockBytes, &tmap_k, &bars->kv_full[stage],
-                        kb * 64, jb * kTileK, hkv, b);
+            tma_load_4d(dst + kb * kKVBlockBytes, tma, &bars->kv_full[stage], kb * 64,
+                        ja * kTileK, hkv, b);
+          if (jb >= 0) {
+#pragma unroll
+            for (int kb = 0; kb < kBlocksD; ++kb)
+              tma_load_4d(dst + kKVTileBytes + kb * kKVBlockBytes, &tmap_k,
+                          &bars->kv_full[stage], kb * 64, jb * kTileK, hkv, b);
+          }
         }
+        __syncwarp();
       };
       if (hi > lo) {
         load_pair(&tmap_k, lo, lo + 1 < hi ? lo + 1 : -1);
@@ -414,8 +424,11 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     // Two issuing threads halve the per-instruction issue overhead; the tensor pipe serialises
     // the two independent streams. Both walk the same K/V ring and both release every stage
     // (kv_empty counts two arrivals), whether or not their tile used it.
-    if (lane == 0 && hi > lo) {
+    // The whole warp runs the loop (every lane waits on the barriers); the elected lane alone
+    // issues MMAs and commits.
+    if (hi > lo) {
       const int t = warp - kMmaWarp0;
+      const bool elected = elect_one_sync();
       bool ok = true;
       if (has_work[t] && !mbar_wait(&bars->q_full[t], 0)) {
         report_timeout(p.status, 2);
@@ -449,22 +462,28 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         const int buf = (j - lo_t[t]) & 1;
         const uint64_t kd = kdesc0 + static_cast<uint64_t>(stage * kStageUnits + half * kHalfUnits);
         const uint32_t d = s_col + buf * 64;
+        if (elected) {
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          mma_ss(d, qdesc + static_cast<uint64_t>((ks / 4) * (kQBlockBytes >> 4) + (ks % 4) * 2),
-                 kd + static_cast<uint64_t>((ks / 4) * (kKVBlockBytes >> 4) + (ks % 4) * 2),
-                 kIdescQK, ks > 0 ? 1u : 0u);
+          for (int ks = 0; ks < D / 16; ++ks) {
+            mma_ss(d, qdesc + static_cast<uint64_t>((ks / 4) * (kQBlockBytes >> 4) + (ks % 4) * 2),
+                   kd + static_cast<uint64_t>((ks / 4) * (kKVBlockBytes >> 4) + (ks % 4) * 2),
+                   kIdescQK, ks > 0 ? 1u : 0u);
+          }
+          tc_commit(&bars->s_full[t][buf]);
         }
-        tc_commit(&bars->s_full[t][buf]);
+        __syncwarp();
       };
       auto issue_pv = [&](int stage, int kt) {
         const uint64_t vd = vdesc0 + static_cast<uint64_t>(stage * kStageUnits);
         const uint32_t a = s_col + (kt & 1) * 64;
+        if (elected) {
 #pragma unroll
-        for (int ks = 0; ks < kTileK / 16; ++ks) {
-          mma_ts(o_col, a + ks * 8, vd + static_cast<uint64_t>(ks * (2048 >> 4)), kIdescPV,
-                 (kt > 0 || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < kTileK / 16; ++ks) {
+            mma_ts(o_col, a + ks * 8, vd + static_cast<uint64_t>(ks * (2048 >> 4)), kIdescPV,
+                   (kt > 0 || ks > 0) ? 1u : 0u);
+          }
         }
+        __syncwarp();
       };
 
       // Prologue: scores of the first two KV tiles (one stage).
@@ -474,7 +493,8 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
           tc_fence_after();
           if (active(lo)) issue_qk(stage, 0, lo);
           if (lo + 1 < hi && active(lo + 1)) issue_qk(stage, 1, lo + 1);
-          tc_commit(&bars->kv_empty[stage]);
+          if (elected) tc_commit(&bars->kv_empty[stage]);
+          __syncwarp();
         }
       }
       const int nblk_t = has_work[t] ? hi_t[t] - lo_t[t] : 0;
@@ -493,11 +513,14 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
           issue_pv(st, kt);
           // Completion points the softmax warps may wait on: the second-to-last PV (for a
           // rescale in the last block) and the last PV (for the epilogue).
-          if (kt == nblk_t - 2) tc_commit(&bars->pv_done[t]);
-          if (kt == nblk_t - 1) tc_commit(&bars->o_final[t]);
+          if (elected) {
+            if (kt == nblk_t - 2) tc_commit(&bars->pv_done[t]);
+            if (kt == nblk_t - 1) tc_commit(&bars->o_final[t]);
+          }
         }
         if (j + 2 < hi && active(j + 2)) issue_qk(st, 1, j + 2);
-        tc_commit(&bars->kv_empty[st]);
+        if (elected) tc_commit(&bars->kv_empty[st]);
+        __syncwarp();
       }
     }
   } else {
@@ -548,13 +571,41 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         const bool masked = rel_lo > 0 || rel_hi < kTileK - 1;
 
         if constexpr (MODE == kModeGeneric) {
-          if (p.bias == nullptr) {
+          // The chain is interpreted op by op over the row's 64 scores in registers: one
+          // (warp-uniform) dispatch per op and block, not one per score - the reference compiles
+          // a kernel per chain (loopfuse/codegen.py:454-998), an interpreter has to keep its
+          // dispatch out of the element loop.
+          auto each = [&](auto f) {
 #pragma unroll
             for (int c = 0; c < 2; ++c)
 #pragma unroll
               for (int i = 0; i < 32; ++i)
-                sr[c][i] = __float_as_uint(apply_mods(p.mods, __uint_as_float(sr[c][i]) * p.a));
+                sr[c][i] = __float_as_uint(f(__uint_as_float(sr[c][i])));
+          };
+          auto run_mods = [&](int m_lo, int m_hi) {
+#pragma unroll 1
+            for (int m = m_lo; m < m_hi; ++m) {
+              const float a = p.mods.arg[m];
+              switch (p.mods.op[m]) {
+                case LF_MOD_MUL: each([&](float x) { return x * a; }); break;
+                case LF_MOD_ADD: each([&](float x) { return x + a; }); break;
+                case LF_MOD_TANH: each([&](float x) { return tanhf(x); }); break;
+                case LF_MOD_EXP: each([&](float x) { return __expf(x); }); break;
+                case LF_MOD_EXP2: each([&](float x) { return exp2f(x); }); break;
+                case LF_MOD_SIN: each([&](float x) { return sinf(x); }); break;
+                case LF_MOD_COS: each([&](float x) { return cosf(x); }); break;
+                case LF_MOD_RELU: each([&](float x) { return fmaxf(x, 0.f); }); break;
+                case LF_MOD_SQUARE: each([&](float x) { return x * x; }); break;
+                case LF_MOD_DIV: each([&](float x) { return x / a; }); break;
+                default: break;
+              }
+            }
+          };
+          each([&](float x) { return x * p.a; });
+          if (p.bias == nullptr) {
+            run_mods(0, p.mods.n);
           } else {
+            run_mods(0, p.bias_pos);
             // This row's 64 bias values of the block: 128 contiguous bytes, eight 16-byte loads
             // (rows past Sq read the last row, columns past Skv are not read: both are masked
             // or clipped later).
@@ -581,11 +632,10 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
                 for (int e = 0; e < 8; ++e) {
                   const float bv = __uint_as_float((e & 1) ? (w[e >> 1] & 0xffff0000u)
                                                            : (w[e >> 1] << 16));
-                  float sv = __uint_as_float(sr[c][i8 * 8 + e]) * p.a;
-                  sv = apply_mods_range(p.mods, sv, 0, p.bias_pos) + bv;
-                  sr[c][i8 * 8 + e] = __float_as_uint(apply_mods_range(p.mods, sv, p.bias_pos, LF_MAX_MODS));
+                  sr[c][i8 * 8 + e] = __float_as_uint(__uint_as_float(sr[c][i8 * 8 + e]) + bv);
                 }
               }
+            run_mods(p.bias_pos, p.mods.n);
           }
         }
 
@@ -672,91 +722,62 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         }
         const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
 
-        // Pass 2: p = exp2(score * c2 - m), two elements per packed instruction.
-        const uint64_t neg_m2 = pack2(-m_safe, -m_safe);
-        uint64_t psum2[4] = {0ull, 0ull, 0ull, 0ull};
+        // Pass 2: p = exp2(score * c2 - m). Plain fp32 instructions and every exp2 on MUFU: the
+        // loop is bound by instruction issue, and the packed f32x2 forms (fewer instructions,
+        // but slower in their pipe) and an FMA-pipe emulation of part of the exp2 both measured
+        // slower than this in the fixed-reference kernel, which runs the same arithmetic.
+        const float neg_m = -m_safe;
+        float ps[4] = {0.f, 0.f, 0.f, 0.f};
         uint32_t pk[32];
-        // One pair in four takes its exponentials on the FMA pipe instead of MUFU (which is the
-        // busiest pipe of this loop): 2^z = 2^n * 2^f with n = round(z) taken from the low
-        // mantissa bits of z + 1.5*2^23, f = z - n in [-0.5, 0.5] and a cubic for 2^f (relative
-        // error 7.5e-5, far below the bf16 rounding of P); n is added into the exponent field.
-        const uint64_t magic2 = pack2(12582912.f, 12582912.f);
-        const uint64_t neg_magic2 = pack2(-12582912.f, -12582912.f);
-        const uint64_t minus_one2 = pack2(-1.f, -1.f);
-        const uint64_t e0 = pack2(0.99992811f, 0.99992811f), e1 = pack2(0.69326099f, 0.69326099f);
-        const uint64_t e2 = pack2(0.24261054f, 0.24261054f), e3 = pack2(0.05517132f, 0.05517132f);
-        auto finish_pair = [&](uint64_t z2, int c, int i, bool apply_mask) {
-          float z0, z1;
-          unpack2(z2, z0, z1);
+        auto finish_pair = [&](float z0, float z1, int c, int i, bool apply_mask) {
           if (apply_mask) {
             const int cc = c * 32 + i;
             if (cc < rel_lo || cc > rel_hi) z0 = -INFINITY;
             if (cc + 1 < rel_lo || cc + 1 > rel_hi) z1 = -INFINITY;
           }
-          float p0, p1;
-          if (((c * 16 + (i >> 1)) & 3) == 3) {
-            const uint64_t zc2 = pack2(fmaxf(z0, -120.f), fmaxf(z1, -120.f));
-            const uint64_t r2 = add2(zc2, magic2);
-            const uint64_t f2 = fma2(add2(r2, neg_magic2), minus_one2, zc2);
-            uint64_t q2 = fma2(f2, e3, e2);
-            q2 = fma2(q2, f2, e1);
-            q2 = fma2(q2, f2, e0);
-            float q0, q1, r0, r1;
-            unpack2(q2, q0, q1);
-            unpack2(r2, r0, r1);
-            p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23));
-            p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
-            if (apply_mask) {  // the clamp above would leave 2^-120 in a masked position
-              if (z0 == -INFINITY) p0 = 0.f;
-              if (z1 == -INFINITY) p1 = 0.f;
-            }
-          } else {
-            p0 = ex2_approx(z0);
-            p1 = ex2_approx(z1);
-          }
-          psum2[(c * 2 + (i >> 1)) & 3] = add2(psum2[(c * 2 + (i >> 1)) & 3], pack2(p0, p1));
+          const float p0 = ex2_approx(z0), p1 = ex2_approx(z1);
+          ps[(c * 2 + (i >> 1)) & 3] += p0;
+          ps[(c * 2 + (i >> 1) + 2) & 3] += p1;
           pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
         };
         if (MODE == kModeSoftcap && tanh_path < 2) {
           // tanh(x) = x*(1 + y*(-1/3 + y*(2/15 + y*(-17/315)))), y = x^2, x = a*raw; the powers
           // of a are folded into the coefficients so that the polynomial runs on raw^2.
           const float a2 = p.a * p.a;
-          const uint64_t b1 = pack2(-a2 / 3.f, -a2 / 3.f);
-          const uint64_t one2 = pack2(1.f, 1.f);
-          const uint64_t ac2 = pack2(p.a * p.c2, p.a * p.c2);
+          const float b1 = -a2 / 3.f;
+          const float ac = p.a * p.c2;
           if (tanh_path == 0) {
             auto body = [&](bool apply_mask) {
 #pragma unroll
               for (int c = 0; c < 2; ++c)
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                  const uint64_t r2 = pack2u(sr[c][i], sr[c][i + 1]);
-                  const uint64_t q2 = fma2(mul2(r2, r2), b1, one2);
-                  finish_pair(fma2(mul2(r2, ac2), q2, neg_m2), c, i, apply_mask);
+                  const float r0 = __uint_as_float(sr[c][i]), r1 = __uint_as_float(sr[c][i + 1]);
+                  const float q0 = fmaf(r0 * r0, b1, 1.f), q1 = fmaf(r1 * r1, b1, 1.f);
+                  finish_pair(fmaf(r0 * ac, q0, neg_m), fmaf(r1 * ac, q1, neg_m), c, i,
+                              apply_mask);
                 }
             };
             if (masked) body(true); else body(false);
           } else {
-            const uint64_t b2 = pack2(a2 * a2 * (2.f / 15.f), a2 * a2 * (2.f / 15.f));
-            const uint64_t b3 =
-                pack2(a2 * a2 * a2 * (-17.f / 315.f), a2 * a2 * a2 * (-17.f / 315.f));
+            const float b2 = a2 * a2 * (2.f / 15.f);
+            const float b3 = a2 * a2 * a2 * (-17.f / 315.f);
             auto body = [&](bool apply_mask) {
 #pragma unroll
               for (int c = 0; c < 2; ++c)
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                  const uint64_t r2 = pack2u(sr[c][i], sr[c][i + 1]);
-                  const uint64_t y2 = mul2(r2, r2);
-                  uint64_t q2 = fma2(y2, b3, b2);
-                  q2 = fma2(q2, y2, b1);
-                  q2 = fma2(q2, y2, one2);
-                  finish_pair(fma2(mul2(r2, ac2), q2, neg_m2), c, i, apply_mask);
+                  const float r0 = __uint_as_float(sr[c][i]), r1 = __uint_as_float(sr[c][i + 1]);
+                  const float y0 = r0 * r0, y1 = r1 * r1;
+                  const float q0 = fmaf(fmaf(fmaf(y0, b3, b2), y0, b1), y0, 1.f);
+                  const float q1 = fmaf(fmaf(fmaf(y1, b3, b2), y1, b1), y1, 1.f);
+                  finish_pair(fmaf(r0 * ac, q0, neg_m), fmaf(r1 * ac, q1, neg_m), c, i,
+                              apply_mask);
                 }
             };
             if (masked) body(true); else body(false);
           }
         } else if constexpr (MODE == kModeSoftcap) {
-          const uint64_t c22 = pack2(p.c2, p.c2);
           auto body = [&](bool apply_mask) {
 #pragma unroll
             for (int c = 0; c < 2; ++c)
@@ -764,25 +785,22 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
               for (int i = 0; i < 32; i += 2) {
                 const float t0 = tanh_approx(__uint_as_float(sr[c][i]) * p.a);
                 const float t1 = tanh_approx(__uint_as_float(sr[c][i + 1]) * p.a);
-                finish_pair(fma2(pack2(t0, t1), c22, neg_m2), c, i, apply_mask);
+                finish_pair(fmaf(t0, p.c2, neg_m), fmaf(t1, p.c2, neg_m), c, i, apply_mask);
               }
           };
           if (masked) body(true); else body(false);
         } else {
-          const uint64_t c22 = pack2(p.c2, p.c2);
           auto body = [&](bool apply_mask) {
 #pragma unroll
             for (int c = 0; c < 2; ++c)
 #pragma unroll
               for (int i = 0; i < 32; i += 2)
-                finish_pair(fma2(pack2u(sr[c][i], sr[c][i + 1]), c22, neg_m2), c, i, apply_mask);
+                finish_pair(fmaf(__uint_as_float(sr[c][i]), p.c2, neg_m),
+                            fmaf(__uint_as_float(sr[c][i + 1]), p.c2, neg_m), c, i, apply_mask);
           };
           if (masked) body(true); else body(false);
         }
-        float ps[8];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) unpack2(psum2[c], ps[2 * c], ps[2 * c + 1]);
-        const float psum = ((ps[0] + ps[1]) + (ps[2] + ps[3])) + ((ps[4] + ps[5]) + (ps[6] + ps[7]));
+        const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
         l_run = l_run * alpha + psum;
         tmem_st_32x32b_x32(s_addr, pk);
         tmem_wait_st();
