@@ -58,6 +58,8 @@ typedef enum {
 #define LF_DEV_OK 0
 #define LF_DEV_TIMEOUT 1        /* a bounded mbarrier wait gave up; low bits say which      */
 #define LF_DEV_BAD_PAGE 2       /* block_table entry outside [0, n_pages)                   */
+#define LF_DEV_BOUNDS 3         /* debug-bounds build only: an index left its range; bits 8..
+                                   say where. The access was skipped or clamped.            */
 
 /* Mask kinds (what the capture layer deduces from loopfuse::causal_mask / sliding_mask). */
 #define LF_MASK_NONE 0
@@ -282,6 +284,14 @@ int lf_selftest_wait_timeout(int64_t limit_cycles, int32_t* status, int64_t* wai
  * [0, n_pages), is reported as LF_DEV_BAD_PAGE in `status` and that row is not written (the
  * kernel never stores outside the pools). Rows of different sequences must not share a page. */
 int lf_kv_append_bf16(const LfKvAppendArgs* args, void* stream);
+
+/* 1 when the library was built with -DLF_DEBUG_BOUNDS (python -m loopfuse_b200.build
+ * --debug-bounds -> liblf_sm100_dbg.so): every index that a kernel forms for a plain global
+ * load or store - token, page slot, staged page-table entry, workspace row, output row - is then
+ * compared with its range first; a violation writes LF_DEV_BOUNDS | (site << 8) to the call's
+ * `status` word and the access is clamped or skipped, nothing traps. Stands in for
+ * compute-sanitizer's memcheck where that tool cannot be used. 0 in the normal build. */
+int lf_debug_bounds(void);
 
 /* Elementwise out = a + b on bf16 [B, H, S, D] tensors (innermost stride 1, 16-byte aligned rows,
  * D % 8 == 0), each with its own element strides of (b, h, s); `out` may alias `a` or `b`. One

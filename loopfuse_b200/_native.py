@@ -5,6 +5,7 @@ Loading fails loudly: there is no Python or CPU substitute for the kernels.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "liblf_sm100.so"
@@ -17,7 +18,7 @@ EXPORTS = [
     "lf_decode_bf16", "lf_decode_paged_bf16", "lf_decode_auto_splits",
     "lf_decode_workspace_bytes", "lf_combine_f32", "lf_paged_gather_bf16",
     "lf_decode_bf16_static", "lf_prefill_kv_tile", "lf_tile_map_cache_stats",
-    "lf_kv_append_bf16", "lf_selftest_wait_timeout", "lf_add_bf16",
+    "lf_kv_append_bf16", "lf_selftest_wait_timeout", "lf_add_bf16", "lf_debug_bounds",
 ]
 
 LF_STATIC_SCRATCH_BYTES = 8 << 20
@@ -86,11 +87,18 @@ def load() -> C.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not LIB_PATH.exists():
+    path = LIB_PATH
+    if os.environ.get("LF_DEBUG_BOUNDS", "0") not in ("", "0"):
+        # the range-checking build of the same sources (python -m loopfuse_b200.build
+        # --debug-bounds); results are the same, violations show up in the status word
+        path = LIB_PATH.with_name("liblf_sm100_dbg.so")
+    if not path.exists():
         raise RuntimeError(
-            f"{LIB_PATH} is missing: build it with `python -m loopfuse_b200.build` "
+            f"{path} is missing: build it with `python -m loopfuse_b200.build` "
             "(needs nvcc). There is no fallback implementation.")
-    lib = C.CDLL(str(LIB_PATH))
+    lib = C.CDLL(str(path))
+    lib.lf_debug_bounds.argtypes = []
+    lib.lf_debug_bounds.restype = C.c_int
     lib.lf_query.argtypes = [C.POINTER(LfDeviceInfo)]
     lib.lf_query.restype = C.c_int
     lib.lf_strerror.argtypes = [C.c_int]

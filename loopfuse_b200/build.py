@@ -1,8 +1,10 @@
 """Build liblf_sm100.so (the C-ABI kernel library) in-tree with nvcc for sm_100a.
 
-Usage: ``python -m loopfuse_b200.build [--force] [--verbose]``. The build needs only nvcc; it
-cross-compiles on hosts without a GPU. The library is written next to this file so that it
-travels with the source tree.
+Usage: ``python -m loopfuse_b200.build [--force] [--verbose] [--debug-bounds]``. The build needs
+only nvcc; it cross-compiles on hosts without a GPU. The library is written next to this file so
+that it travels with the source tree. ``--debug-bounds`` builds the same sources with
+``-DLF_DEBUG_BOUNDS`` into ``liblf_sm100_dbg.so`` (index range checks that report through the
+status word; loaded instead of the normal library when ``LF_DEBUG_BOUNDS=1`` is set).
 """
 from __future__ import annotations
 
@@ -17,6 +19,8 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "liblf_sm100.so"
 STAMP_PATH = PKG_DIR / "csrc" / ".build_stamp"
+DBG_LIB_PATH = PKG_DIR / "liblf_sm100_dbg.so"
+DBG_STAMP_PATH = PKG_DIR / "csrc" / ".build_stamp_dbg"
 
 PUBLIC_HEADER = PKG_DIR.parent / "include" / "lf_sm100.h"
 
@@ -57,19 +61,24 @@ def _fingerprint() -> str:
     return h.hexdigest()
 
 
-def build_native(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every .cu under csrc/ into liblf_sm100.so; skip when sources are unchanged."""
+def build_native(force: bool = False, verbose: bool = False,
+                 debug_bounds: bool = False) -> Path:
+    """Compile every .cu under csrc/ into liblf_sm100.so (or, with ``debug_bounds``, into
+    liblf_sm100_dbg.so with -DLF_DEBUG_BOUNDS); skip when sources are unchanged."""
     fp = _fingerprint()
-    if not force and LIB_PATH.exists() and STAMP_PATH.exists() and STAMP_PATH.read_text() == fp:
-        return LIB_PATH
+    lib_path, stamp_path = (DBG_LIB_PATH, DBG_STAMP_PATH) if debug_bounds else (LIB_PATH, STAMP_PATH)
+    flags = NVCC_FLAGS + (["-DLF_DEBUG_BOUNDS"] if debug_bounds else [])
+    suffix = ".dbg.o" if debug_bounds else ".o"
+    if not force and lib_path.exists() and stamp_path.exists() and stamp_path.read_text() == fp:
+        return lib_path
     nvcc = _nvcc()
     objs = []
     log = []
     procs = []
     for path in _sources():
         src = path.name
-        obj = path.with_suffix(".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-c", str(path), "-o", str(obj)]
+        obj = path.with_suffix(suffix)
+        cmd = [nvcc, *flags, "-c", str(path), "-o", str(obj)]
         procs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE,
                                                  stderr=subprocess.STDOUT, text=True)))
     for src, obj, proc in procs:
@@ -78,17 +87,18 @@ def build_native(force: bool = False, verbose: bool = False) -> Path:
         if proc.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}:\n{out}")
         objs.append(str(obj))
-    cmd = [nvcc, "-shared", "-o", str(LIB_PATH), *objs, "-lcudart"]
+    cmd = [nvcc, "-shared", "-o", str(lib_path), *objs, "-lcudart"]
     out = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if out.returncode != 0:
         raise RuntimeError(f"link failed:\n{out.stdout}")
-    (CSRC / "build.log").write_text("\n".join(log))
-    STAMP_PATH.write_text(fp)
+    (CSRC / ("build_dbg.log" if debug_bounds else "build.log")).write_text("\n".join(log))
+    stamp_path.write_text(fp)
     if verbose:
         print("\n".join(log))
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
-    path = build_native(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    path = build_native(force="--force" in sys.argv, verbose="--verbose" in sys.argv,
+                        debug_bounds="--debug-bounds" in sys.argv)
     print(path)

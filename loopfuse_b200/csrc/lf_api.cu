@@ -42,6 +42,14 @@ __global__ void selftest_wait_kernel(long long limit_cycles, int32_t* status, lo
 
 extern "C" {
 
+int lf_debug_bounds(void) {
+#ifdef LF_DEBUG_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
+}
+
 int lf_selftest_wait_timeout(int64_t limit_cycles, int32_t* status, int64_t* waited_cycles,
                              void* stream) {
   if (limit_cycles <= 0 || limit_cycles > 2000000000ll || !status) return LF_ERR_INVALID_ARG;

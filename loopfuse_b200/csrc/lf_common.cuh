@@ -154,6 +154,18 @@ __device__ __forceinline__ float apply_mods(const ModChain& mc, float s) {
   return s;
 }
 
+// Range check of the debug-bounds build: LF_BOUNDS(cond, status, site) is `cond`, and records a
+// violation in the status word; in the normal build it is the constant true and costs nothing.
+#ifdef LF_DEBUG_BOUNDS
+__device__ __forceinline__ bool bounds_ok(bool ok, int32_t* status, int site) {
+  if (!ok && status) atomicCAS(status, 0, LF_DEV_BOUNDS | (site << 8));
+  return ok;
+}
+#define LF_BOUNDS(cond, status, site) ::lf::bounds_ok((cond), (status), (site))
+#else
+#define LF_BOUNDS(cond, status, site) (true)
+#endif
+
 // One lane of the (converged) warp is elected; the others get false. A role whose work is issued
 // by a single lane (tcgen05.mma, TMA) should still run its loop with the whole warp converged
 // and guard only the issuing instructions with this predicate: a warp that has diverged into a

@@ -144,13 +144,18 @@ __global__ void __launch_bounds__(kDecodeThreads)
     for (int u = 0; u < U; ++u) {
       const int t = base + u * RPW + rg;
       valid[u] = t < t1;
-      const int tc = valid[u] ? t : (t1 - 1);  // clamp: the row is loaded but scored -inf
+      int tc = valid[u] ? t : (t1 - 1);  // clamp: the row is loaded but scored -inf
+      if (!LF_BOUNDS(tc >= t0 && tc < p.Skv, p.status, 40)) tc = t0;
       int64_t koff, voff;
       if constexpr (PAGED) {
         const int pg_abs = p.page_shift >= 0 ? (tc >> p.page_shift) : (tc / p.page_size);
         const int slot = tc - pg_abs * p.page_size;
-        const int64_t pgk = s_pages_k[pg_abs - first_page];
-        const int64_t pgv = s_pages_v[pg_abs - first_page];
+        int pl = pg_abs - first_page;
+        if (!LF_BOUNDS(pl >= 0 && pl < n_pages_local && slot >= 0 && slot < p.page_size,
+                       p.status, 41))
+          pl = 0;
+        const int64_t pgk = s_pages_k[pl];
+        const int64_t pgv = s_pages_v[pl];
         koff = pgk * p.k_stride[0] + slot * p.k_stride[1];
         voff = pgv * p.v_stride[0] + slot * p.v_stride[1];
       } else {
@@ -388,10 +393,16 @@ __global__ void __launch_bounds__(WARPS * 32, 12 / WARPS)
     kbase = p.k + b * p.k_stride[0] + kvh * p.k_stride[1];
     vbase = p.v + b * p.v_stride[0] + kvh * p.v_stride[1];
   }
+  [[maybe_unused]] const int n_pages_staged =
+      (PAGED && t1 > t0) ? page_of(t1 - 1) - first_page + 1 : 0;
   auto k_row = [&](int t) -> const __nv_bfloat16* {
+    if (!LF_BOUNDS(t >= t0 && t < t1 && t < p.Skv, p.status, 42)) t = t0;
     if constexpr (PAGED) {
       const int pg_abs = page_of(t);
       const int slot = t - pg_abs * p.page_size;
+      if (!LF_BOUNDS(pg_abs - first_page >= 0 && pg_abs - first_page < n_pages_staged,
+                     p.status, 43))
+        return kbase;
       return kbase + static_cast<int64_t>(s_pages_k[pg_abs - first_page]) * p.k_stride[0] +
              slot * p.k_stride[1];
     } else {
@@ -399,9 +410,13 @@ __global__ void __launch_bounds__(WARPS * 32, 12 / WARPS)
     }
   };
   auto v_row = [&](int t) -> const __nv_bfloat16* {
+    if (!LF_BOUNDS(t >= t0 && t < t1 && t < p.Skv, p.status, 44)) t = t0;
     if constexpr (PAGED) {
       const int pg_abs = page_of(t);
       const int slot = t - pg_abs * p.page_size;
+      if (!LF_BOUNDS(pg_abs - first_page >= 0 && pg_abs - first_page < n_pages_staged,
+                     p.status, 45))
+        return vbase;
       return vbase + static_cast<int64_t>(s_pages_v[pg_abs - first_page]) * p.v_stride[0] +
              slot * p.v_stride[1];
     } else {
@@ -454,6 +469,9 @@ __global__ void __launch_bounds__(WARPS * 32, 12 / WARPS)
           const int r = lane / CPR + q * (32 / CPR);
           const int rc = min(r, r_max);
           const uint32_t off = r * kRowBytes + ((j ^ (r & 7)) << 4);
+          if (!LF_BOUNDS(off + 16 <= 16u * kRowBytes && stage >= 0 && stage < kMmaStages,
+                         p.status, 46))
+            continue;
           cp_async_16(dst0 + off, kp + rc * ks);
           cp_async_16(dst0 + 16 * kRowBytes + off, vp + rc * vs);
         }
@@ -600,6 +618,8 @@ __global__ void __launch_bounds__(WARPS * 32, 12 / WARPS)
       acc += src[cc] * a;
     }
     const int64_t unit = (static_cast<int64_t>(b) * p.Hkv + kvh) * G + gg;
+    if (!LF_BOUNDS(gg < G && cc < D && b < p.B && kvh < p.Hkv && split < p.splits, p.status, 47))
+      continue;
     if (p.splits == 1) {
       __nv_bfloat16* op = p.out + b * p.o_stride[0] + kvh * p.o_stride[1] + gg * p.o_stride[2];
       op[cc] = __float2bfloat16_rn(acc / l_all);

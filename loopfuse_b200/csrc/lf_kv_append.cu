@@ -54,6 +54,9 @@ __global__ void __launch_bounds__(256) kv_append_kernel(const KvAppendParams p) 
       if (p.status) atomicExch(p.status, LF_DEV_BAD_PAGE);
       continue;
     }
+    if (!LF_BOUNDS(b < p.B && h < p.Hkv && t < p.T && c < CPR && slot >= 0 && slot < p.page_size,
+                   p.status, 50))
+      continue;
     const uint4 kx = ldg_stream_16(p.k_new + b * p.kn_stride[0] + h * p.kn_stride[1] +
                                    static_cast<int64_t>(t) * p.kn_stride[2] + c * 8);
     const uint4 vx = ldg_stream_16(p.v_new + b * p.vn_stride[0] + h * p.vn_stride[1] +

@@ -618,7 +618,9 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
               for (int i8 = 0; i8 < 4; ++i8) {
                 const int cc = c * 32 + i8 * 8;
                 uint32_t w[4] = {0u, 0u, 0u, 0u};
-                if (c0 + cc + 8 <= p.Skv) {
+                if (c0 + cc + 8 <= p.Skv &&
+                    LF_BOUNDS(c0 + cc >= 0 && b < static_cast<int>(gridDim.z) && h < p.Hq,
+                              p.status, 60)) {
                   const uint4 v4 = ldg_stream_16(brow + cc);
                   w[0] = v4.x; w[1] = v4.y; w[2] = v4.z; w[3] = v4.w;
                 } else {
