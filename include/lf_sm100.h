@@ -208,7 +208,13 @@ const char* lf_last_cuda_error(void);
  * accumulators can overflow where the running-max form would not. Every other chain uses the
  * running-max kernel. The persistent kernel keeps its work-queue counters in the library image
  * (256 slots taken round-robin and zeroed in stream order): more than 256 such launches in
- * flight at once on one device could share a counter. */
+ * flight at once on one device could share a counter. A launch recorded into a CUDA graph keeps
+ * the slot it was given at capture time for as long as the graph lives, while eager launches
+ * keep cycling through the slots: keep replays of such a graph and eager launches of the
+ * persistent kernel on one stream (or ordered), or every 256th eager launch could share the
+ * replay's counter and lose work items. The first call of each kernel variant (head dim,
+ * score-function mode) on a host thread sets kernel attributes and looks up symbol addresses:
+ * make it outside stream capture, from the thread that will capture. */
 int lf_prefill_bf16(const LfPrefillArgs* args, void* stream);
 /* KV tile size (64 or 128 keys) of the kernel lf_prefill_bf16 would run for these arguments, or
  * a negative LfStatus; launches nothing. Skip ranges and `dbg_ranges` are in units of it.
