@@ -11,12 +11,12 @@ TFLOP/s with the causal-adjusted FLOP count of the reference's benchmark
 
 N > 1 (launched by torchrun, one rank per GPU, NCCL): (batch x kv-head) units are independent, so
 every rank owns its own batch of 8 sequences ("weak" scaling) and computes with no collective in
-the data path; the output slabs of EVERY step are then gathered with one NCCL all-gather per
-step, issued on a second stream so that the gather of step i overlaps the kernel of step i+1.
-`value` is the whole-job rate of that pipelined loop; the kernel-only rate, the cost of a gather
-alone and the overlapped step time are reported next to it, the gathered tensor is verified
-against the ranks' own slabs, and the strong-scaling view (one batch of 8 split over the ranks)
-is reported under `strong_scaling`.
+the data path; `value` is the units of all ranks over the max-over-ranks time of K steps of that
+sharded compute, and does not depend on K. What it costs to also replicate every step's output
+on every rank is measured next to it and kept out of `value`: one NCCL all-gather of the output
+slabs per step on a second stream (`with_gather_every_step`, the gather alone, its bus
+bandwidth), the gathered tensor verified against the ranks' own slabs. The strong-scaling view
+(one batch of 8 split over the ranks) is reported under `strong_scaling`.
 
 One JSON line is printed by rank 0. Besides the contract keys it carries
   roofline      achieved vs measured peak of the dominant kernel (CUDA-event timed here)
@@ -468,8 +468,13 @@ def run_ours(args, workload) -> None:
     ms_per_step = kernel_ms
     collective = "none"
     if world > 1 and not args.kernel_only:
-        # ---- the path's one collective: all-gather of the output slabs, once per step, on a
-        # second stream: the gather of step i overlaps the kernel of step i+1.
+        # ---- not part of `value`: what it costs to ALSO replicate every step's output on every
+        # rank - an all-gather of the output slabs once per step on a second stream, the gather
+        # of step i next to the kernel of step i+1. The path itself has no exchange step (the
+        # (batch x kv-head) units are independent and a consumer of sharded attention output,
+        # e.g. the output projection under tensor parallelism, reads the local slab), so `value`
+        # is the rate of the sharded compute; these keys say what a caller who wants the full
+        # tensor everywhere pays on top.
         # (With one CTA of the persistent prefill kernel resident on every SM the collective's
         # kernel cannot start before it ends, so the two serialise. `--sm-margin` leaves SMs
         # free, but NCCL's all-gather needs ~26 of them for its full rate: not worth it.)
@@ -512,7 +517,6 @@ def run_ours(args, workload) -> None:
         barrier()
         overlapped_ms, gather_ms = max_over_ranks(
             [s1.elapsed_time(e1) / steps, s2.elapsed_time(e2) / steps], dev, world)
-        ms_per_step = overlapped_ms
         launches += (steps + 3) * runners[0].launches_per_call
         # Every slab of the gathered tensor equals the owning rank's output, bit for bit:
         # compare position-weighted integer checksums of the slabs.
@@ -530,11 +534,15 @@ def run_ours(args, workload) -> None:
             "gather_ms_per_step": gather_ms, "overlapped_ms_per_step": overlapped_ms,
             "gather_bus_gbs": slab_bytes * (world - 1) / 1e9 / (gather_ms * 1e-3),
             "gather_verified": bool(torch.equal(got, all_mine)),
+            "with_gather_every_step": {"value": world * work / (overlapped_ms * 1e-3),
+                                       "unit": unit, "ms_per_step": overlapped_ms},
             "sm_margin": args.sm_margin,
         })
-        collective = ("one all-gather of the output slabs per step on a second stream, "
-                      "overlapping the next step's kernel; `value` = whole-job rate of that "
-                      "pipelined loop (see kernel_only_per_gpu, gather_ms_per_step)")
+        collective = ("none in the data path: `value` = units of all ranks / max-over-ranks time "
+                      "of the sharded kernels, independent of --steps. Replicating every step's "
+                      "output on every rank (one all-gather per step on a second stream) is "
+                      "measured separately: with_gather_every_step, gather_ms_per_step, "
+                      "overlapped_ms_per_step, gather_bus_gbs, gather_verified")
         del gathered, slabs, weights
 
         # ---- strong scaling: ONE batch of the configuration split over the ranks
