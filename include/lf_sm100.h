@@ -41,7 +41,7 @@
 extern "C" {
 #endif
 
-#define LF_ABI_VERSION 4
+#define LF_ABI_VERSION 5
 
 typedef enum {
   LF_OK = 0,
@@ -132,6 +132,16 @@ typedef struct {
   const void* score_bias;
   int64_t bias_stride[3];
   int32_t bias_pos;
+  /* Second score product (NULL = none): scores = scale * (q k^T + q_pe k_pe^T), the two-matmul
+   * form of the reference's MLA test (tests/test_attention.py:126-151). q_pe bf16 [B, Hq, Sq,
+   * D_pe], k_pe bf16 [B, Hkv, Skv, D_pe], D_pe in {8, 16, ..., 64}, innermost stride 1, rows
+   * 16-byte aligned. Dense K/V, no score bias, and a mod chain of constant multipliers only
+   * (anything else is LF_ERR_UNSUPPORTED). */
+  const void* q_pe;
+  const void* k_pe;
+  int64_t qpe_stride[3];
+  int64_t kpe_stride[3];
+  int32_t D_pe;
 } LfPrefillArgs;
 
 typedef struct {

@@ -39,6 +39,8 @@ class LfPrefillArgs(C.Structure):
         ("page_size", C.c_int32), ("n_pages", C.c_int32),
         ("sm_margin", C.c_int32),
         ("score_bias", C.c_void_p), ("bias_stride", C.c_int64 * 3), ("bias_pos", C.c_int32),
+        ("q_pe", C.c_void_p), ("k_pe", C.c_void_p), ("qpe_stride", C.c_int64 * 3),
+        ("kpe_stride", C.c_int64 * 3), ("D_pe", C.c_int32),
     ]
 
 

@@ -161,8 +161,9 @@ class CompiledAttention:
         is_decode = (spec.mask_kind == MASK_NONE and decode_rows in _DECODE_GROUPS
                      and (Sq == 1 or group == 1) and (both_paged or not
                                                       (spec.k.paged or spec.v.paged)))
-        if spec.q_bias is not None or spec.out_bias is not None or spec.score_bias is not None:
-            is_decode = False   # the bias tensors are read by the prefill kernel only
+        if (spec.q_bias is not None or spec.out_bias is not None or spec.score_bias is not None
+                or spec.q_pe is not None):
+            is_decode = False   # bias tensors / a second score product: prefill kernel only
         if is_decode:
             kernel = "paged_decode" if both_paged else "decode"
         else:
@@ -241,6 +242,14 @@ class CompiledAttention:
                 mods=plan.mods, mask_kind=spec.mask_kind, window=plan.window, status=status,
                 k_block_table=args[spec.k.block_table] if spec.k.paged else None,
                 v_block_table=args[spec.v.block_table] if spec.v.paged else None)
+        elif spec.q_pe is not None:
+            # Two-matmul (MLA-style) scores, tests/test_attention.py:126-151 of the reference.
+            out = F.prefill_attention(
+                q, args[spec.k.placeholder], args[spec.v.placeholder], scale=plan.scale,
+                mods=plan.mods, mask_kind=spec.mask_kind, window=plan.window, status=status,
+                q_pe=args[spec.q_pe], k_pe=args[spec.k_pe])
+            if spec.out_bias is not None:
+                F.add_bf16(out, args[spec.out_bias], out=out)
         elif spec.q_bias is not None or spec.out_bias is not None or spec.score_bias is not None:
             # Modified attention of the reference's tests (tests/test_accuracy.py:176-194): the
             # query bias is added first (one bf16 rounding, as in the eager graph), the score

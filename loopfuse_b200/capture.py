@@ -9,7 +9,9 @@ graphs directly, walking back from the graph output:
     M     = [causal_mask | sliding_mask]* ( score-mod chain ( view(bmm(Q', K'^T)) ) )
     optionally with the additive tensors of the reference's modified attention
     (tests/test_accuracy.py:176-194): out + out_bias, (Q + q_bias), and one `+ scores_bias`
-    ([B,H,S,S]) anywhere in the score-mod chain
+    ([B,H,S,S]) anywhere in the score-mod chain; and with the two-matmul scores of its MLA test
+    (tests/test_attention.py:126-151): view(bmm(Q, K^T)) + view(bmm(Q_pe, K_pe^T)) at the start
+    of the chain
     K',V' = dense input, optionally through repeat_interleave (unsqueeze -> expand -> clone -> view)
             or a paged gather  paged_load(pool, table) [-> view merging page dims] -> transpose(1, 2)
 
@@ -214,7 +216,19 @@ class _Matcher:
         mods: list[ScoreMod] = []
         score_bias = None
         ops_after_bias = 0
-        while not (_is(node, *_VIEW_LIKE) and _is(node.args[0], aten.bmm.default)):
+        def is_qk(n):
+            return _is(n, *_VIEW_LIKE) and _is(n.args[0], aten.bmm.default)
+
+        pe_qk = None
+        while not is_qk(node):
+            if (_is(node, aten.add.Tensor) and is_qk(node.args[0]) and is_qk(node.args[1])):
+                # Q K^T + Q_pe K_pe^T: the main product is the one whose width V shares
+                node, pe_qk = node.args[0], node.args[1]
+                v_width = self.placeholders[v_src.placeholder].meta["val"].shape[-1]
+                width = lambda n: self._strip_bmm_operand(n.args[0].args[0]).meta["val"].shape[-1]
+                if width(node) != v_width and width(pe_qk) == v_width:
+                    node, pe_qk = pe_qk, node
+                break
             if _is(node, *_CASTS):
                 # dtype round trips of the eager bf16 graph; the kernels keep scores in fp32
                 # (the reference strips them too: cleanup_passes.py:211-271)
@@ -291,6 +305,24 @@ class _Matcher:
             if dt != torch.bfloat16:
                 raise NotImplementedError(
                     f"{what} has dtype {dt}; the sm_100a kernels take bfloat16 inputs")
+        q_pe = k_pe = None
+        if pe_qk is not None:
+            pq = self._strip_bmm_operand(pe_qk.args[0].args[0])
+            pkt = self._strip_bmm_operand(pe_qk.args[0].args[1])
+            if not _is_transpose(pkt, 2, 3):
+                raise NotImplementedError("second score product is not Q_pe @ K_pe.transpose(-2, -1)")
+            q_pe = self._tensor_placeholder(pq, "Q_pe")
+            k_pe = self._tensor_placeholder(pkt.args[0], "K_pe")
+            for idx in (q_pe, k_pe):
+                if self.placeholders[idx].meta["val"].dtype != torch.bfloat16:
+                    raise NotImplementedError("Q_pe / K_pe must be bfloat16")
+            if (k_src.paged or v_src.paged or k_src.repeated or q_bias is not None
+                    or score_bias is not None):
+                raise NotImplementedError(
+                    "two-product scores are supported with dense, ungrouped K/V and no bias")
+            if any(m.op not in (MOD_MUL, MOD_DIV) for m in mods):
+                raise NotImplementedError(
+                    "two-product scores take constant multipliers only between QK^T and the mask")
         biases = [i for i in (q_bias, out_bias, score_bias) if i is not None]
         for idx in biases:
             if self.placeholders[idx].meta["val"].dtype != torch.bfloat16:
@@ -300,7 +332,7 @@ class _Matcher:
         return AttentionSpec(q=q_idx, k=k_src, v=v_src, mods=tuple(mods), mask_kind=mask_kind,
                              windows=tuple(windows), n_args=len(self.placeholders),
                              q_bias=q_bias, out_bias=out_bias, score_bias=score_bias,
-                             bias_pos=len(mods) - ops_after_bias)
+                             bias_pos=len(mods) - ops_after_bias, q_pe=q_pe, k_pe=k_pe)
 
 
 def _describe(node: Any) -> str:

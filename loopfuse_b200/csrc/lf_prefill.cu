@@ -136,6 +136,7 @@ struct PrefillParams {
   int64_t kp_stride[3], vp_stride[3];  // (page, slot, kv head)
   int64_t bt_stride;
   int32_t page_size, page_shift, n_pages;
+  int32_t pe_steps;  // PE variant: 16-column steps of the second score product (D_pe / 16, rounded up)
 };
 
 // Barrier block at the start of shared memory.
@@ -155,17 +156,33 @@ __device__ __forceinline__ void report_timeout(int32_t* status, int where) {
   if (status) atomicCAS(status, LF_DEV_OK, LF_DEV_TIMEOUT | (where << 8));
 }
 
-template <int D, int MODE>
+// `PE`: scores are the sum of two products, Q K^T + Q_pe K_pe^T (the two-matmul form of the
+// reference's MLA test, tests/test_attention.py:126-151: a "nope" part of width D and a rotary
+// part of width D_pe <= 64). The second pair of operands rides along as one more 64-column
+// swizzle block behind the D/64 blocks of every Q and K tile - TMA zero-fills the columns past
+// D_pe - and the QK^T loop issues its k-steps after the others into the same accumulator. K tiles
+// are then larger than V tiles; a ring slot has the size of a K tile.
+template <int D, bool PE>
+struct PrefillStages {
+  static constexpr int value = PE ? (D == 64 ? 4 : 2) : StagesFor<D>::value;
+};
+
+template <int D, int MODE, bool PE>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
     prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
                    const __grid_constant__ CUtensorMap tmap_k,
-                   const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
-  constexpr int kStages = StagesFor<D>::value;
+                   const __grid_constant__ CUtensorMap tmap_v,
+                   const __grid_constant__ CUtensorMap tmap_qpe,
+                   const __grid_constant__ CUtensorMap tmap_kpe, const PrefillParams p) {
+  constexpr int kStages = PrefillStages<D, PE>::value;
   constexpr int kBlocksD = D / 64;                    // 64-column swizzle blocks per tile row
+  constexpr int kBlocksQK = kBlocksD + (PE ? 1 : 0);  // ... of a Q or K tile
   constexpr uint32_t kQBlockBytes = kTileQ * 128;     // one [128][64] bf16 block of Q
-  constexpr uint32_t kQTileBytes = kQBlockBytes * kBlocksD;
+  constexpr uint32_t kQTileBytes = kQBlockBytes * kBlocksQK;
   constexpr uint32_t kKVBlockBytes = kTileK * 128;    // one [64][64] bf16 block of K or V
-  constexpr uint32_t kKVTileBytes = kKVBlockBytes * kBlocksD;
+  constexpr uint32_t kVTileBytes = kKVBlockBytes * kBlocksD;
+  constexpr uint32_t kKTileBytes = kKVBlockBytes * kBlocksQK;
+  constexpr uint32_t kKVTileBytes = kKTileBytes;      // size of a ring slot (two per stage)
   constexpr uint32_t kIdescQK = make_idesc_bf16(128, kTileK, 0);
   constexpr uint32_t kIdescPV = make_idesc_bf16(128, D, 1);
   constexpr uint32_t kColO = 256;
@@ -379,6 +396,9 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
           for (int kb = 0; kb < kBlocksD; ++kb)
             tma_load_4d(sQ + t * kQTileBytes + kb * kQBlockBytes, &tmap_q, &bars->q_full[t],
                         kb * 64, (iq0 + t) * kTileQ, h, b);
+          if constexpr (PE)
+            tma_load_4d(sQ + t * kQTileBytes + kBlocksD * kQBlockBytes, &tmap_qpe,
+                        &bars->q_full[t], 0, (iq0 + t) * kTileQ, h, b);
         }
         __syncwarp();
       }
@@ -398,18 +418,25 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
           return;
         }
         if (elected) {
-          mbar_arrive_expect_tx(&bars->kv_full[stage],
-                                jb >= 0 ? 2 * kKVTileBytes : kKVTileBytes);
+          const bool a_is_k = tma == &tmap_k;
+          mbar_arrive_expect_tx(&bars->kv_full[stage], (a_is_k ? kKTileBytes : kVTileBytes) +
+                                                           (jb >= 0 ? kKTileBytes : 0u));
           unsigned char* dst = sKV + stage * (2 * kKVTileBytes);
 #pragma unroll
           for (int kb = 0; kb < kBlocksD; ++kb)
             tma_load_4d(dst + kb * kKVBlockBytes, tma, &bars->kv_full[stage], kb * 64,
+                        ja * kTileK, hkv, b);
+          if (PE && a_is_k)
+            tma_load_4d(dst + kBlocksD * kKVBlockBytes, &tmap_kpe, &bars->kv_full[stage], 0,
                         ja * kTileK, hkv, b);
           if (jb >= 0) {
 #pragma unroll
             for (int kb = 0; kb < kBlocksD; ++kb)
               tma_load_4d(dst + kKVTileBytes + kb * kKVBlockBytes, &tmap_k,
                           &bars->kv_full[stage], kb * 64, jb * kTileK, hkv, b);
+            if constexpr (PE)
+              tma_load_4d(dst + kKVTileBytes + kBlocksD * kKVBlockBytes, &tmap_kpe,
+                          &bars->kv_full[stage], 0, jb * kTileK, hkv, b);
           }
         }
         __syncwarp();
@@ -468,6 +495,12 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
             mma_ss(d, qdesc + static_cast<uint64_t>((ks / 4) * (kQBlockBytes >> 4) + (ks % 4) * 2),
                    kd + static_cast<uint64_t>((ks / 4) * (kKVBlockBytes >> 4) + (ks % 4) * 2),
                    kIdescQK, ks > 0 ? 1u : 0u);
+          }
+          if constexpr (PE) {  // + Q_pe K_pe^T: the extra block of both tiles, same accumulator
+            for (int ks = 0; ks < p.pe_steps; ++ks)
+              mma_ss(d, qdesc + static_cast<uint64_t>(kBlocksD * (kQBlockBytes >> 4) + ks * 2),
+                     kd + static_cast<uint64_t>(kBlocksD * (kKVBlockBytes >> 4) + ks * 2),
+                     kIdescQK, 1u);
           }
           tc_commit(&bars->s_full[t][buf]);
         }
@@ -992,19 +1025,21 @@ static int make_tile_map(CUtensorMap* map, const void* base, int B, int H, int S
   return LF_OK;
 }
 
-template <int D, int MODE>
+template <int D, int MODE, bool PE = false>
 static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                          const PrefillParams& p, int B, cudaStream_t st) {
-  constexpr size_t kQTileBytes = static_cast<size_t>(kTileQ) * D * 2;
-  constexpr size_t kKVTileBytes = static_cast<size_t>(kTileK) * D * 2;
+                          const PrefillParams& p, int B, cudaStream_t st,
+                          const CUtensorMap* mqpe = nullptr, const CUtensorMap* mkpe = nullptr) {
+  constexpr size_t kQTileBytes = static_cast<size_t>(kTileQ) * (D + (PE ? 64 : 0)) * 2;
+  constexpr size_t kKVTileBytes = static_cast<size_t>(kTileK) * (D + (PE ? 64 : 0)) * 2;
   constexpr size_t smem = 1024 /*align slack*/ + 1024 /*barriers*/ + kStageBytesTotal +
                           2 * kQTileBytes +
-                          StagesFor<D>::value * 2 * kKVTileBytes;
+                          PrefillStages<D, PE>::value * 2 * kKVTileBytes;
+  static_assert(smem <= 232448, "shared memory of a CTA");
   static thread_local int configured_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_dev != dev) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_kernel<D, MODE>,
+    cudaError_t e = cudaFuncSetAttribute(prefill_kernel<D, MODE, PE>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
     if (e != cudaSuccess) {
@@ -1019,7 +1054,9 @@ static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CU
   PrefillParams pp = p;
   pp.single = (p.n_qtiles > 1 && static_cast<int64_t>(pairs) * p.Hq * B < sm_count) ? 1 : 0;
   dim3 grid(pp.single ? p.n_qtiles : pairs, p.Hq, B);
-  prefill_kernel<D, MODE><<<grid, kPrefillThreads, smem, st>>>(mq, mk, mv, pp);
+  // (without a second score product the two extra maps are never read)
+  prefill_kernel<D, MODE, PE><<<grid, kPrefillThreads, smem, st>>>(mq, mk, mv, mqpe ? *mqpe : mq,
+                                                                   mkpe ? *mkpe : mk, pp);
   return check_launch("prefill_kernel");
 }
 
@@ -1207,6 +1244,16 @@ static int prefill_impl(const LfPrefillArgs* a, void* const* launch) {
     p.mods.op[i] = 0;
     p.mods.arg[i] = 0.f;
   }
+  p.pe_steps = 0;
+  const bool has_pe = a->q_pe != nullptr || a->k_pe != nullptr;
+  if (has_pe) {
+    if (!a->q_pe || !a->k_pe) return LF_ERR_INVALID_ARG;
+    if (a->D_pe <= 0 || a->D_pe > 64 || a->D_pe % 8) return LF_ERR_UNSUPPORTED;
+    if (p.paged || a->score_bias) return LF_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(a->q_pe) | reinterpret_cast<uintptr_t>(a->k_pe)) & 15u)
+      return LF_ERR_ALIGNMENT;
+    p.pe_steps = (a->D_pe + 15) / 16;
+  }
   p.bias = static_cast<const __nv_bfloat16*>(a->score_bias);
   p.bias_pos = a->bias_pos;
   for (int i = 0; i < 3; ++i) p.bias_stride[i] = a->bias_stride[i];
@@ -1272,6 +1319,11 @@ static int prefill_impl(const LfPrefillArgs* a, void* const* launch) {
     }
   }
 
+  if (has_pe) {
+    // The two-product form runs in the plain running-max mode only (scale, then mask).
+    if (mode == kModeBounded || mode == kModeSoftcap || mode == kModeGeneric)
+      return LF_ERR_UNSUPPORTED;
+  }
   const int kv_tile = choose_kv_tile(a, mode);
   if (kv_tile < 0) return kv_tile;
   if (launch == nullptr) return kv_tile;  // query only
@@ -1299,6 +1351,17 @@ static int prefill_impl(const LfPrefillArgs* a, void* const* launch) {
   }
 
   cudaStream_t st = static_cast<cudaStream_t>(*launch);
+  if (has_pe) {
+    // Boxes of 64 columns over tensors of D_pe columns: the columns past D_pe arrive as zeros.
+    CUtensorMap mqpe, mkpe;
+    rc = make_tile_map(&mqpe, a->q_pe, a->B, a->Hq, a->Sq, a->D_pe, a->qpe_stride, kTileQ);
+    if (rc != LF_OK) return rc;
+    rc = make_tile_map(&mkpe, a->k_pe, a->B, a->Hkv, a->Skv, a->D_pe, a->kpe_stride, kTileK);
+    if (rc != LF_OK) return rc;
+    if (a->D == 128)
+      return launch_prefill<128, kModeNone, true>(mq, mk, mv, p, a->B, st, &mqpe, &mkpe);
+    return launch_prefill<64, kModeNone, true>(mq, mk, mv, p, a->B, st, &mqpe, &mkpe);
+  }
   if (a->D == 128) {
     if (mode == kModeNone) return launch_prefill<128, kModeNone>(mq, mk, mv, p, a->B, st);
     if (mode == kModeSoftcap) return launch_prefill<128, kModeSoftcap>(mq, mk, mv, p, a->B, st);

@@ -78,12 +78,18 @@ def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scal
                       v_block_table: Optional[torch.Tensor] = None,
                       seq_len: Optional[int] = None,
                       score_bias: Optional[torch.Tensor] = None,
-                      bias_pos: Optional[int] = None) -> torch.Tensor:
+                      bias_pos: Optional[int] = None,
+                      q_pe: Optional[torch.Tensor] = None,
+                      k_pe: Optional[torch.Tensor] = None) -> torch.Tensor:
     """softmax(mask(mods(scale * q k^T))) v for q [B,Hq,Sq,D], k/v [B,Hkv,Skv,D] (bf16).
 
     ``score_bias`` (bf16 ``[B, Hq, Sq, Skv]``) is added to the scores after the first
     ``bias_pos`` ops of ``mods`` (default: after all of them) and before the mask; the kernel
     reads it tile by tile (dense k / v only).
+
+    ``q_pe`` ``[B, Hq, Sq, D_pe]`` and ``k_pe`` ``[B, Hkv, Skv, D_pe]`` (bf16, D_pe a multiple of
+    8 up to 64) add a second product to the scores: ``scale * (q k^T + q_pe k_pe^T)``, the
+    two-matmul (MLA-style) form; ``mods`` may then hold constant multipliers only.
 
     With ``k_block_table`` (``v_block_table``), ``k`` (``v``) is a paged pool
     ``[pages, page_size, Hkv, D]`` (or ``[pages, Hkv, D]``, one token per page) read through that
@@ -106,6 +112,20 @@ def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scal
         for i in range(3):
             a.bias_stride[i] = score_bias.stride(i)
         a.bias_pos = a.n_mod if bias_pos is None else int(bias_pos)
+    if (q_pe is None) != (k_pe is None):
+        raise ValueError("q_pe and k_pe go together")
+    if q_pe is not None:
+        _require_cuda(q_pe, k_pe)
+        _check_bf16_lastdim(q_pe, "q_pe")
+        _check_bf16_lastdim(k_pe, "k_pe")
+        if (q_pe.dim() != 4 or k_pe.dim() != 4 or q_pe.shape[:3] != q.shape[:3]
+                or tuple(k_pe.shape[:3]) != (a.B, a.Hkv, a.Skv) or q_pe.shape[3] != k_pe.shape[3]):
+            raise ValueError(f"q_pe {tuple(q_pe.shape)} / k_pe {tuple(k_pe.shape)} do not fit "
+                             f"q {tuple(q.shape)} and the keys")
+        a.q_pe, a.k_pe, a.D_pe = q_pe.data_ptr(), k_pe.data_ptr(), q_pe.shape[3]
+        for i in range(3):
+            a.qpe_stride[i] = q_pe.stride(i)
+            a.kpe_stride[i] = k_pe.stride(i)
     with torch.cuda.device(dev):
         rc = _native.load().lf_prefill_bf16(C.byref(a), _stream_ptr(dev))
     _native.check(rc, "lf_prefill_bf16")

@@ -83,6 +83,10 @@ class AttentionSpec:
     out_bias: Optional[int] = None    # ... added to the output
     score_bias: Optional[int] = None  # ... of a [B,Hq,Sq,Skv] tensor added to the scores
     bias_pos: int = 0                 # the score bias is added after this many ops of ``mods``
+    # Second score product of the MLA-style graph (tests/test_attention.py:126-151):
+    # scores = Q K^T + Q_pe K_pe^T; flat argument indices of Q_pe and K_pe
+    q_pe: Optional[int] = None
+    k_pe: Optional[int] = None
 
     @property
     def window(self) -> int:

@@ -18,6 +18,7 @@ What each function follows (paths inside tomatillos/loopfuse):
                       328-334, 481-484 and tests/test_accuracy.py:131-135
   modified_attention_ref   the function of tests/test_accuracy.py:176-181 (query, score and output
                       bias), with the two bf16 roundings its eager graph has around the matmuls
+  mla_attention_ref   the two-matmul scores of tests/test_attention.py:126-134
   kv_append_ref       the inverse of paged_load_ref: the cache / table convention of
                       tests/benchmark.py:308-319 read by loopfuse/torch_backend/__init__.py:46-56,
                       used as an indexed store (pool[block_table[b, t // P], t % P] = new row)
@@ -190,6 +191,21 @@ def modified_attention_ref(q, k, v, q_bias, scores_bias, out_bias, *, mult: floa
         outs.append(torch.softmax(s, dim=-1) @ v[b0:b0 + batch_chunk])
     att = torch.cat(outs).to(torch.bfloat16).float()
     return att + out_bias.float().cpu()
+
+
+def mla_attention_ref(q, q_pe, k, k_pe, v, *, mask: str = "causal",
+                      batch_chunk: int = 1) -> torch.Tensor:
+    """softmax(mask((Q K^T + Q_pe K_pe^T) * (D + D_pe)^-0.5)) V in fp32 on the CPU."""
+    q, q_pe, k, k_pe, v = (t.float().cpu() for t in (q, q_pe, k, k_pe, v))
+    scale = (q.shape[-1] + q_pe.shape[-1]) ** -0.5
+    outs = []
+    for b0 in range(0, q.shape[0], batch_chunk):
+        sl = slice(b0, b0 + batch_chunk)
+        s = (q[sl] @ k[sl].transpose(-2, -1) + q_pe[sl] @ k_pe[sl].transpose(-2, -1)) * scale
+        if mask == "causal":
+            s = causal_mask_general(s)
+        outs.append(torch.softmax(s, dim=-1) @ v[sl])
+    return torch.cat(outs)
 
 
 def softcap_mods(c: float) -> list:

@@ -168,6 +168,26 @@ def test_modified_attention_of_the_reference_tests_is_captured():
     assert spec.bias_pos == 2          # after `* D ** -0.5` and `* 3.5` of the captured chain
 
 
+def test_two_matmul_scores_of_the_reference_mla_test_are_captured():
+    """The graph of the reference's tests/test_attention.py:126-134."""
+    def fn(Q_nope, Q_pe, K_nope, K_pe, V):
+        qk_nope = Q_nope @ K_nope.transpose(-2, -1)
+        qk_pe = Q_pe @ K_pe.transpose(-2, -1)
+        qk = qk_nope + qk_pe
+        qk *= (Q_nope.shape[-1] + Q_pe.shape[-1]) ** (-0.5)
+        masked_qk = torch.ops.loopfuse.causal_mask(qk)
+        return torch.softmax(masked_qk, dim=-1) @ V
+
+    qn = torch.randn(1, 2, 128, 64, dtype=torch.bfloat16)
+    qp = torch.randn(1, 2, 128, 8, dtype=torch.bfloat16)
+    plan = compile_plan(fn, (qn, qp, qn.clone(), qp.clone(), qn.clone()))
+    spec = plan.spec
+    assert plan.kernel == "prefill" and plan.mask_kind == 1 and plan.D == 64
+    assert spec.q_pe is not None and spec.k_pe is not None
+    assert len({spec.q, spec.q_pe, spec.k.placeholder, spec.k_pe, spec.v.placeholder}) == 5
+    assert plan.scale == pytest.approx(72 ** -0.5) and mod_names(plan) == []
+
+
 def test_mode_kwarg_is_accepted():
     w = small("causal_tiny")
     plan = compile_plan(w.fn(), make_inputs(w), mode=None)

@@ -131,6 +131,43 @@ def test_reference_style_modified_attention(S_):
     torch.testing.assert_close(out.float().cpu(), want, atol=2e-2, rtol=2 ** -7)
 
 
+@pytest.mark.parametrize("D,S_", [(128, 1024), (64, 593)])
+def test_reference_style_mla_two_matmul_scores(D, S_):
+    # tests/test_attention.py:126-151: scores = Q_nope K_nope^T + Q_pe K_pe^T with D_pe = D / 8,
+    # scaled by (D + D_pe)^-0.5, causal (the reference only prints the generated code for this
+    # graph; parity here is against the eager fp32 function)
+    def fn(Q_nope, Q_pe, K_nope, K_pe, V):
+        qk_nope = Q_nope @ K_nope.transpose(-2, -1)
+        qk_pe = Q_pe @ K_pe.transpose(-2, -1)
+        qk = qk_nope + qk_pe
+        qk *= (Q_nope.shape[-1] + Q_pe.shape[-1]) ** (-0.5)
+        masked_qk = torch.ops.loopfuse.causal_mask(qk)
+        scores = torch.softmax(masked_qk, dim=-1)
+        return scores @ V
+
+    g = torch.Generator().manual_seed(11)
+    B, H = 2, 4
+    mk = lambda *shape: torch.randn(*shape, generator=g).bfloat16()
+    Qn, Kn, V = (mk(B, H, S_, D) for _ in range(3))
+    Qp, Kp = mk(B, H, S_, D // 8), mk(B, H, S_, D // 8)
+    out = compile_and_run(fn, (Qn, Qp, Kn, Kp, V))
+    want = O.mla_attention_ref(Qn, Qp, Kn, Kp, V, batch_chunk=B)
+    assert (out.float().cpu() - want).abs().max().item() <= TOL
+
+
+def test_second_score_product_with_a_wide_rotary_part():
+    """C-ABI level: D_pe = 48 (three k-steps of the extra block), no mask, Sq != Skv."""
+    from loopfuse_b200 import functional as F
+    g = torch.Generator().manual_seed(12)
+    mk = lambda *shape: torch.randn(*shape, generator=g).bfloat16()
+    q, qp = mk(1, 2, 130, 128), mk(1, 2, 130, 48)
+    k, kp, v = mk(1, 2, 300, 128), mk(1, 2, 300, 48), mk(1, 2, 300, 128)
+    out = F.prefill_attention(q.cuda(), k.cuda(), v.cuda(), scale=176 ** -0.5, q_pe=qp.cuda(),
+                              k_pe=kp.cuda())
+    want = O.mla_attention_ref(q, qp, k, kp, v, mask="none")
+    assert (out.float().cpu() - want).abs().max().item() <= TOL
+
+
 def test_score_bias_position_in_the_chain():
     """C-ABI level: the bias is added after `bias_pos` ops of the chain (here between a tanh and
     a multiplier), not at its end."""
