@@ -17,7 +17,7 @@ EXPORTS = [
     "lf_query", "lf_strerror", "lf_last_cuda_error", "lf_prefill_bf16", "lf_skip_range",
     "lf_decode_bf16", "lf_decode_paged_bf16", "lf_decode_auto_splits",
     "lf_decode_workspace_bytes", "lf_combine_f32", "lf_paged_gather_bf16",
-    "lf_decode_bf16_static", "lf_prefill_kv_tile", "lf_tile_map_cache_stats",
+    "lf_decode_bf16_static", "lf_prefill_kv_tile", "lf_prefill_q_tile", "lf_tile_map_cache_stats",
     "lf_kv_append_bf16", "lf_selftest_wait_timeout", "lf_add_bf16", "lf_debug_bounds",
 ]
 
@@ -109,6 +109,8 @@ def load() -> C.CDLL:
     lib.lf_last_cuda_error.restype = C.c_char_p
     lib.lf_prefill_bf16.argtypes = [C.POINTER(LfPrefillArgs), C.c_void_p]
     lib.lf_prefill_bf16.restype = C.c_int
+    lib.lf_prefill_q_tile.argtypes = [C.POINTER(LfPrefillArgs)]
+    lib.lf_prefill_q_tile.restype = C.c_int
     lib.lf_prefill_kv_tile.argtypes = [C.POINTER(LfPrefillArgs)]
     lib.lf_prefill_kv_tile.restype = C.c_int
     lib.lf_tile_map_cache_stats.argtypes = [C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]

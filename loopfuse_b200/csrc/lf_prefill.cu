@@ -1067,7 +1067,7 @@ constexpr int kTicketSlots = 256;
 static __device__ unsigned int g_prefill_tickets[kTicketSlots];
 static std::atomic<unsigned int> g_next_ticket_slot{0};
 
-template <int D>
+template <int D, bool PACKED = false>
 static int launch_prefill_bounded(const CUtensorMap& mq, const CUtensorMap& mk,
                                   const CUtensorMap& mv, const CUtensorMap& mo, PrefillParams p,
                                   int B, cudaStream_t st) {
@@ -1081,7 +1081,7 @@ static int launch_prefill_bounded(const CUtensorMap& mq, const CUtensorMap& mk,
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_dev != dev) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_bounded_kernel<D>,
+    cudaError_t e = cudaFuncSetAttribute(prefill_bounded_kernel<D, PACKED>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
     if (e == cudaSuccess)
@@ -1093,14 +1093,18 @@ static int launch_prefill_bounded(const CUtensorMap& mq, const CUtensorMap& mk,
     }
     configured_dev = dev;
   }
+  // Packed layout: the query rows are walked in chunks of 32 (p.n_qtiles counts those) and an
+  // item is a pair of chunks of one kv head, for all of its query heads at once.
+  const int heads = PACKED ? p.Hq / p.group : p.Hq;
+  if (PACKED) p.n_qtiles = (p.Sq + 31) / 32;
   p.n_pairs = (p.n_qtiles + 1) / 2;
   p.n_deferred = (p.mask_kind == LF_MASK_CAUSAL && p.Sq == p.Skv) ? p.n_pairs / 4 : 0;
-  p.main_items = static_cast<int32_t>(static_cast<int64_t>(p.n_pairs - p.n_deferred) * p.Hq * B);
+  p.main_items = static_cast<int32_t>(static_cast<int64_t>(p.n_pairs - p.n_deferred) * heads * B);
   p.div_main = FastDiv::make(p.n_pairs - p.n_deferred);
   p.div_deferred = FastDiv::make(p.n_deferred > 0 ? p.n_deferred : 1);
-  p.div_hq = FastDiv::make(p.Hq);
+  p.div_hq = FastDiv::make(heads);
   p.div_group = FastDiv::make(p.group);
-  const int64_t n_items = static_cast<int64_t>(p.n_pairs) * p.Hq * B;
+  const int64_t n_items = static_cast<int64_t>(p.n_pairs) * heads * B;
   if (n_items > 0x7fffffff - 4096) return LF_ERR_TOO_LARGE;
   p.n_items = static_cast<int32_t>(n_items);
   p.ticket = tickets + g_next_ticket_slot.fetch_add(1) % kTicketSlots;
@@ -1111,7 +1115,7 @@ static int launch_prefill_bounded(const CUtensorMap& mq, const CUtensorMap& mk,
   }
   const int ctas = sm_count - p.sm_margin > 0 ? sm_count - p.sm_margin : 1;
   const int grid = static_cast<int>(n_items < ctas ? n_items : ctas);
-  prefill_bounded_kernel<D><<<grid, kBoundedThreads, smem, st>>>(mq, mk, mv, mo, p);
+  prefill_bounded_kernel<D, PACKED><<<grid, kBoundedThreads, smem, st>>>(mq, mk, mv, mo, p);
   return check_launch("prefill_bounded_kernel");
 }
 
@@ -1174,7 +1178,7 @@ static int choose_kv_tile(const LfPrefillArgs* a, int mode) {
 }
 
 // `launch` == nullptr: only resolve the kernel choice and return its KV tile size.
-static int prefill_impl(const LfPrefillArgs* a, void* const* launch) {
+static int prefill_impl(const LfPrefillArgs* a, void* const* launch, int* q_tile = nullptr) {
   if (!a || !a->q || !a->k || !a->v || !a->out) return LF_ERR_INVALID_ARG;
   if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Sq <= 0 || a->Skv <= 0)
     return LF_ERR_INVALID_ARG;
@@ -1326,10 +1330,15 @@ static int prefill_impl(const LfPrefillArgs* a, void* const* launch) {
   }
   const int kv_tile = choose_kv_tile(a, mode);
   if (kv_tile < 0) return kv_tile;
+  // Four query heads per kv head under a window mask: the packed layout of the fixed-reference
+  // kernel (32 query rows of each of the four heads per tile slot).
+  const bool packed = mode == kModeBounded && kv_tile != kWideK && p.group == 4 &&
+                      a->mask_kind == LF_MASK_CAUSAL_WINDOW;
+  if (q_tile) *q_tile = packed ? 32 : kTileQ;
   if (launch == nullptr) return kv_tile;  // query only
 
   CUtensorMap mq, mk, mv;
-  int rc = make_tile_map(&mq, a->q, a->B, a->Hq, a->Sq, a->D, a->q_stride, kTileQ);
+  int rc = make_tile_map(&mq, a->q, a->B, a->Hq, a->Sq, a->D, a->q_stride, packed ? 32 : kTileQ);
   if (rc != LF_OK) return rc;
   if (p.paged & 1) {
     mk = mq;  // never used: the producer warp gathers K itself
@@ -1367,6 +1376,7 @@ static int prefill_impl(const LfPrefillArgs* a, void* const* launch) {
     if (mode == kModeSoftcap) return launch_prefill<128, kModeSoftcap>(mq, mk, mv, p, a->B, st);
     if (mode == kModeBounded)
       return kv_tile == kWideK ? launch_prefill_wide<128>(mq, mk, mv, mo, p, a->B, st)
+             : packed          ? launch_prefill_bounded<128, true>(mq, mk, mv, mo, p, a->B, st)
                                : launch_prefill_bounded<128>(mq, mk, mv, mo, p, a->B, st);
     return launch_prefill<128, kModeGeneric>(mq, mk, mv, p, a->B, st);
   }
@@ -1374,6 +1384,7 @@ static int prefill_impl(const LfPrefillArgs* a, void* const* launch) {
   if (mode == kModeSoftcap) return launch_prefill<64, kModeSoftcap>(mq, mk, mv, p, a->B, st);
   if (mode == kModeBounded)
     return kv_tile == kWideK ? launch_prefill_wide<64>(mq, mk, mv, mo, p, a->B, st)
+           : packed          ? launch_prefill_bounded<64, true>(mq, mk, mv, mo, p, a->B, st)
                              : launch_prefill_bounded<64>(mq, mk, mv, mo, p, a->B, st);
   return launch_prefill<64, kModeGeneric>(mq, mk, mv, p, a->B, st);
 }
@@ -1387,6 +1398,12 @@ int lf_prefill_bf16(const LfPrefillArgs* args, void* stream) {
 }
 
 int lf_prefill_kv_tile(const LfPrefillArgs* args) { return lf::prefill_impl(args, nullptr); }
+
+int lf_prefill_q_tile(const LfPrefillArgs* args) {
+  int q_tile = 0;
+  const int rc = lf::prefill_impl(args, nullptr, &q_tile);
+  return rc < 0 ? rc : q_tile;
+}
 
 void lf_tile_map_cache_stats(uint64_t* hits, uint64_t* misses) {
   if (hits) *hits = lf::g_tile_map_hits.load();

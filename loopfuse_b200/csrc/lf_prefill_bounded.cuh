@@ -68,8 +68,11 @@ struct ItemGeom {
   __device__ __forceinline__ int hi_t(int t) const { return t ? hi1 : hi0; }
 };
 
+// `rows_q` = query rows one tile slot covers per head: 128, or 32 in the packed layout, where a
+// slot holds 32 rows of each of the four query heads of one kv head (then `h` is the first of
+// the four, the items run over kv heads, and iq0 counts 32-row chunks).
 __device__ __forceinline__ ItemGeom decode_item(const PrefillParams& p, int it,
-                                                int tile_k = kTileK) {
+                                                int tile_k = kTileK, int rows_q = kTileQ) {
   ItemGeom g;
   g.it = it;
   // Heaviest query tiles of a head first. With a causal mask the lightest quarter of the pairs
@@ -86,14 +89,19 @@ __device__ __forceinline__ ItemGeom decode_item(const PrefillParams& p, int it,
     pair = p.n_deferred - 1 - (r - hb * p.n_deferred);
   }
   g.b = static_cast<int>(p.div_hq.div(hb));
-  g.h = hb - g.b * p.Hq;
-  g.hkv = static_cast<int>(p.div_group.div(g.h));
+  if (rows_q == kTileQ) {
+    g.h = hb - g.b * p.Hq;
+    g.hkv = static_cast<int>(p.div_group.div(g.h));
+  } else {  // packed: div_hq divides by the number of kv heads
+    g.hkv = hb - g.b * static_cast<int>(p.div_hq.d);
+    g.h = g.hkv * p.group;
+  }
   g.iq0 = pair * 2;
-  skip_range(p.mask_kind, p.window, p.causal_offset, p.Sq, p.Skv, kTileQ, tile_k, g.iq0, &g.lo0,
+  skip_range(p.mask_kind, p.window, p.causal_offset, p.Sq, p.Skv, rows_q, tile_k, g.iq0, &g.lo0,
              &g.hi0);
-  skip_range(p.mask_kind, p.window, p.causal_offset, p.Sq, p.Skv, kTileQ, tile_k, g.iq0 + 1,
+  skip_range(p.mask_kind, p.window, p.causal_offset, p.Sq, p.Skv, rows_q, tile_k, g.iq0 + 1,
              &g.lo1, &g.hi1);
-  const bool v0 = g.iq0 * kTileQ < p.Sq, v1 = (g.iq0 + 1) * kTileQ < p.Sq;
+  const bool v0 = g.iq0 * rows_q < p.Sq, v1 = (g.iq0 + 1) * rows_q < p.Sq;
   const bool w0 = v0 && g.hi0 > g.lo0, w1 = v1 && g.hi1 > g.lo1;
   g.flags = (v0 ? 1 : 0) | (v1 ? 2 : 0) | (w0 ? 4 : 0) | (w1 ? 8 : 0);
   g.lo = 0;
@@ -111,7 +119,13 @@ __device__ __forceinline__ ItemGeom decode_item(const PrefillParams& p, int it,
   return g;
 }
 
-template <int D>
+// PACKED (grouped-query attention with four query heads per kv head under a window mask): a
+// tile slot holds 32 query rows of each of the four heads instead of 128 rows of one head. The
+// keys a slot needs then span 32 + window - 1 positions instead of 128 + window - 1 (five 64-key
+// blocks instead of six at a window of 256, and six ring stages per item instead of eight), and
+// the four heads share every K/V tile in shared memory, not just in L2. Row r of a slot is row
+// r % 32 of the chunk for head h0 + r / 32: tensor-memory lane quadrant q is head h0 + q.
+template <int D, bool PACKED>
 __global__ void __launch_bounds__(kBoundedThreads, 1)
     prefill_bounded_kernel(const __grid_constant__ CUtensorMap tmap_q,
                            const __grid_constant__ CUtensorMap tmap_k,
@@ -119,6 +133,7 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
                            const __grid_constant__ CUtensorMap tmap_o, const PrefillParams p) {
   constexpr int kStages = StagesFor<D>::value;
   constexpr int kBlocksD = D / 64;
+  constexpr int kRowsQ = PACKED ? 32 : kTileQ;  // query rows of a slot per head
   constexpr uint32_t kQBlockBytes = kTileQ * 128;
   constexpr uint32_t kQTileBytes = kQBlockBytes * kBlocksD;
   constexpr uint32_t kKVBlockBytes = kTileK * 128;
@@ -252,7 +267,7 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
           break;
         }
         ItemGeom g;
-        if (it >= 0) g = decode_item(p, it);
+        if (it >= 0) g = decode_item(p, it, kTileK, kRowsQ);
         else g.it = -1, g.b = g.h = g.hkv = g.iq0 = g.lo0 = g.hi0 = g.lo1 = g.hi1 = g.flags = g.lo = g.hi = 0;
         if (elected) {
           item_slots[slot] = g;
@@ -271,10 +286,19 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
           ++qseq[t];
           if (elected) {
             mbar_arrive_expect_tx(&bars->q_full[t], kQTileBytes);
+            if constexpr (PACKED) {  // four boxes of 32 rows (one per head) per 64-column block
 #pragma unroll
-            for (int kb = 0; kb < kBlocksD; ++kb)
-              tma_load_4d(sQ + t * kQTileBytes + kb * kQBlockBytes, &tmap_q, &bars->q_full[t],
-                          kb * 64, (g.iq0 + t) * kTileQ, g.h, g.b);
+              for (int hq = 0; hq < 4; ++hq)
+#pragma unroll
+                for (int kb = 0; kb < kBlocksD; ++kb)
+                  tma_load_4d(sQ + t * kQTileBytes + kb * kQBlockBytes + hq * (32 * 128), &tmap_q,
+                              &bars->q_full[t], kb * 64, (g.iq0 + t) * 32, g.h + hq, g.b);
+            } else {
+#pragma unroll
+              for (int kb = 0; kb < kBlocksD; ++kb)
+                tma_load_4d(sQ + t * kQTileBytes + kb * kQBlockBytes, &tmap_q, &bars->q_full[t],
+                            kb * 64, (g.iq0 + t) * kTileQ, g.h, g.b);
+            }
           }
           __syncwarp();
         }
@@ -464,10 +488,11 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
     for (int seq = 0; ok; ++seq) {
       const ItemGeom g = next_item(seq, true);
       if (g.it < 0) break;
-      const int grow = (g.iq0 + t) * kTileQ + row;
-      if (p.dbg_ranges && g.valid(t) && row == 0 && half == 0) {
+      const int grow = (g.iq0 + t) * kRowsQ + (PACKED ? lane : row);
+      const int head = PACKED ? g.h + quarter : g.h;
+      if (p.dbg_ranges && g.valid(t) && (PACKED ? lane : row) == 0 && half == 0) {
         const int64_t idx =
-            ((static_cast<int64_t>(g.b) * p.Hq + g.h) * p.n_qtiles + (g.iq0 + t)) * 2;
+            ((static_cast<int64_t>(g.b) * p.Hq + head) * p.n_qtiles + (g.iq0 + t)) * 2;
         p.dbg_ranges[idx] = g.lo_t(t);
         p.dbg_ranges[idx + 1] = g.hi_t(t);
       }
@@ -475,7 +500,7 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
         if (g.valid(t) && grow < p.Sq && half == 0) {
           // No visible key at all for this tile: softmax of an all -inf row is NaN in the
           // eager computation, so the rows are written as NaN.
-          __nv_bfloat16* orow = p.out + g.b * p.o_stride[0] + g.h * p.o_stride[1] +
+          __nv_bfloat16* orow = p.out + g.b * p.o_stride[0] + head * p.o_stride[1] +
                                 static_cast<int64_t>(grow) * p.o_stride[2];
           const uint4 nan4 = {0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u};
 #pragma unroll
@@ -623,7 +648,8 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
       ++wseq;
       tc_fence_after();
       const float inv = 1.f / l_run;
-      const int row0 = (g.iq0 + t) * kTileQ + quarter * 32;  // first global row of the warp
+      // first global row of the warp
+      const int row0 = PACKED ? (g.iq0 + t) * 32 : (g.iq0 + t) * kTileQ + quarter * 32;
       uint32_t orr[D / 64][32];
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) tmem_ld_32x32b_x32(o_addr + half * (D / 2) + c * 32, orr[c]);
@@ -656,7 +682,7 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          tma_store_4d(&tmap_o, stage, half * (D / 2) + c * 32, row0, g.h, g.b);
+          tma_store_4d(&tmap_o, stage, half * (D / 2) + c * 32, row0, head, g.b);
           tma_store_commit();
         }
       }

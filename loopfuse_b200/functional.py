@@ -207,6 +207,20 @@ def prefill_kv_tile(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale:
     return rc
 
 
+def prefill_q_tile(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float = 1.0,
+                   mods: Sequence[ScoreMod] = (), mask_kind: int = MASK_NONE, window: int = 0,
+                   causal_offset: int = 0, kv_tile: int = 0) -> int:
+    """Query rows per head that one tile of the kernel ``prefill_attention`` runs for these
+    arguments covers (128, or 32 in the packed grouped-query layout); ``dbg_ranges`` holds one
+    (lo, hi) per (batch, head, tile of that many rows)."""
+    a, _, _ = _prefill_args(q, k, v, scale, mods, mask_kind, window, causal_offset, q,
+                            None, None, kv_tile, 0)
+    rc = _native.load().lf_prefill_q_tile(C.byref(a))
+    if rc < 0:
+        _native.check(rc, "lf_prefill_q_tile")
+    return rc
+
+
 def _prefill_args(q, k, v, scale, mods, mask_kind, window, causal_offset, out, status,
                   dbg_ranges, kv_tile, sm_margin=0, k_block_table=None, v_block_table=None,
                   seq_len=None):
@@ -273,8 +287,12 @@ def _prefill_args(q, k, v, scale, mods, mask_kind, window, causal_offset, out, s
     _fill_mods(a, scale, mods)
     a.mask_kind, a.window, a.causal_offset = int(mask_kind), int(window), int(causal_offset)
     a.status = status.data_ptr() if status is not None else None
+    a.kv_tile = int(kv_tile)
     if dbg_ranges is not None:
-        need = B * Hq * (-(-Sq // TILE_Q)) * 2
+        q_tile = _native.load().lf_prefill_q_tile(C.byref(a))
+        if q_tile < 0:
+            _native.check(q_tile, "lf_prefill_q_tile")
+        need = B * Hq * (-(-Sq // q_tile)) * 2
         if dbg_ranges.dtype != torch.int32 or dbg_ranges.numel() < need or not dbg_ranges.is_cuda:
             raise ValueError(f"dbg_ranges must be a CUDA int32 tensor with >= {need} elements")
         a.dbg_ranges = dbg_ranges.data_ptr()

@@ -309,18 +309,22 @@ def test_persistent_softcap_kernel_iterates_exactly_the_analysed_skip_ranges(kin
     items than SMs, so every CTA walks several items), in units of the kernel's own KV tile."""
     B, H, D = 3, 32, 64
     q, k, v = _prefill_case(B, H, 8, S_, S_, D)
-    n_qt = -(-S_ // S.TILE_Q)
-    dbg = torch.full((B * H * n_qt * 2,), -1, dtype=torch.int32, device=DEV)
     kw = dict(scale=0.125, mods=SOFTCAP, mask_kind=kind, window=W, kv_tile=kv_tile)
     assert F.prefill_kv_tile(q.to(DEV), k.to(DEV), v.to(DEV), **kw) == kv_tile
+    # Four query heads per kv head: under a window mask the 64-key kernel packs them into one
+    # tile and walks the query rows in chunks of 32; the ranges are then per chunk.
+    q_tile = F.prefill_q_tile(q.to(DEV), k.to(DEV), v.to(DEV), **kw)
+    assert q_tile == (32 if kind == S.MASK_CAUSAL_WINDOW and kv_tile == 64 else S.TILE_Q)
+    n_qt = -(-S_ // q_tile)
+    dbg = torch.full((B * H * n_qt * 2,), -1, dtype=torch.int32, device=DEV)
     _run_prefill(q, k, v, dbg_ranges=dbg, **kw)
     got = dbg.view(B * H, n_qt, 2).cpu()
-    table = S.skip_table(kind, W, 0, S_, S_, tile_k=kv_tile)
+    table = S.skip_table(kind, W, 0, S_, S_, tile_q=q_tile, tile_k=kv_tile)
     mask = {S.MASK_NONE: "none", S.MASK_CAUSAL: "causal", S.MASK_CAUSAL_WINDOW: "window"}[kind]
     keep = O.keep_matrix(mask, W, S_, S_)
     for iq in range(n_qt):
         assert all(tuple(got[u, iq].tolist()) == table[iq] for u in range(B * H))
-        assert table[iq] == O.brute_force_skip_range(mask, W, S_, S_, S.TILE_Q, kv_tile, iq,
+        assert table[iq] == O.brute_force_skip_range(mask, W, S_, S_, q_tile, kv_tile, iq,
                                                      keep=keep)
 
 
