@@ -650,21 +650,38 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
       const float inv = 1.f / l_run;
       // first global row of the warp
       const int row0 = PACKED ? (g.iq0 + t) * 32 : (g.iq0 + t) * kTileQ + quarter * 32;
-      uint32_t orr[D / 64][32];
-#pragma unroll
-      for (int c = 0; c < D / 64; ++c) tmem_ld_32x32b_x32(o_addr + half * (D / 2) + c * 32, orr[c]);
-      tmem_wait_ld();
-      // O_t is in registers: the first PV of the next item may overwrite it.
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->o_free[t]);
       // The warp's 32 rows x 32 columns go to its staging buffer in the 64-byte swizzle of the
       // output tensor map (16-byte piece q of row r at position q ^ ((r >> 1) & 3), conflict
       // free), and one bulk tensor store moves them to global memory; rows past Sq are clipped
       // by the hardware. The store engine, not the load/store unit of the SM, writes the
       // 32 x 64-byte row segments.
+      // Long items (kLoadAll): all of the warp's O columns are loaded first, so that O_t is
+      // released as early as possible. Short items (the packed layout): one 32-column box at a
+      // time, so that the tensor-memory load of the next box runs while the store engine reads
+      // the previous one out of the staging buffer (measured: +1.5 % there, -0.5 % on long items).
+      constexpr bool kLoadAll = !PACKED;
+      uint32_t orr[D / 64][32];
+      if constexpr (kLoadAll) {
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tmem_ld_32x32b_x32(o_addr + half * (D / 2) + c * 32, orr[c]);
+        tmem_wait_ld();
+        // O_t is in registers: the first PV of the next item may overwrite it.
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->o_free[t]);
+      }
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
+        if constexpr (!kLoadAll) {
+          tmem_ld_32x32b_x32(o_addr + half * (D / 2) + c * 32, orr[c]);
+          tmem_wait_ld();
+          if (c == D / 64 - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->o_free[t]);
+          }
+        }
         if (c > 0) {  // the previous box must have been read before the buffer is refilled
           if (lane == 0) tma_store_wait_read();
           __syncwarp();
