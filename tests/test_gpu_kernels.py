@@ -242,7 +242,8 @@ def test_prefill_softcap(S_, scale_in, kv_tile):
 
 @pytest.mark.parametrize("kv_tile", KV_TILES)
 @pytest.mark.parametrize("S_,W,G", [(1024, 256, 4), (593, 130, 2), (640, 258, 1), (300, 1024, 4),
-                                    (512, 1, 1), (2048, 256, 4), (900, 64, 2)])
+                                    (512, 1, 1), (2048, 256, 4), (900, 64, 2),
+                                    (593, 130, 4), (45, 16, 4), (97, 300, 4)])
 def test_prefill_window_gqa_softcap(S_, W, G, kv_tile):
     q, k, v = _prefill_case(1, 2 * G, 2, S_, S_, 128, scale=2.0)
     out = _run_prefill(q, k, v, scale=128 ** -0.5, mods=SOFTCAP,
@@ -337,6 +338,19 @@ def test_prefill_softcap_head_dim_64(S_, W, kv_tile):
                        kv_tile=kv_tile)
     want = O.attention_ref(q, k, v, mods=O.softcap_mods(50.0), mask="window" if W else "causal",
                            window=W, batch_chunk=2)
+    assert max_err(out, want) <= TOL
+
+
+@pytest.mark.parametrize("S_,W", [(1024, 200), (333, 96)])
+def test_prefill_packed_gqa_layout_head_dim_64(S_, W):
+    """Four query heads per kv head under a window mask at D = 64: the packed layout (32 rows of
+    each head per tile), ragged sizes, more than one kv head and batch."""
+    q, k, v = _prefill_case(2, 8, 2, S_, S_, 64, scale=1.5)
+    kw = dict(scale=64 ** -0.5, mods=SOFTCAP, mask_kind=S.MASK_CAUSAL_WINDOW, window=W)
+    assert F.prefill_q_tile(q.to(DEV), k.to(DEV), v.to(DEV), **kw) == 32
+    out = _run_prefill(q, k, v, **kw)
+    want = O.attention_ref(q, k, v, mods=O.softcap_mods(50.0), mask="window", window=W,
+                           batch_chunk=2)
     assert max_err(out, want) <= TOL
 
 
