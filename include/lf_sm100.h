@@ -230,11 +230,11 @@ int lf_prefill_bf16(const LfPrefillArgs* args, void* stream);
  * a negative LfStatus; launches nothing. Skip ranges and `dbg_ranges` are in units of it.
  * Replaces the tile sizes the reference autotunes per kernel (loopfuse/codegen.py:360-393). */
 int lf_prefill_kv_tile(const LfPrefillArgs* args);
-/* Query rows per head that one tile of that kernel covers: LF_PREFILL_TILE_Q, or 32 when the
- * library packs the four query heads of a kv head into one tile (grouped-query attention with
- * Hq / Hkv == 4 under a window mask and a softcap chain). `dbg_ranges` then holds one (lo, hi)
- * per (batch, query head, 32-row chunk): int32 [B * Hq * ceil(Sq / 32) * 2]. Negative LfStatus
- * on error; launches nothing. */
+/* Query rows per head that one tile of that kernel covers: LF_PREFILL_TILE_Q, or 128 / g when
+ * the library packs the g = Hq / Hkv query heads of a kv head into one tile (grouped-query
+ * attention with g in {2, 4} under a window mask and a softcap chain). `dbg_ranges` then holds
+ * one (lo, hi) per (batch, query head, chunk of that many rows): int32 [B * Hq * ceil(Sq /
+ * q_tile) * 2]. Negative LfStatus on error; launches nothing. */
 int lf_prefill_q_tile(const LfPrefillArgs* args);
 /* Hit / miss counters of the library's cache of encoded tensor maps (keyed by address, shape,
  * strides and box; the per-call host work the reference's launcher repeats on every call,

@@ -1067,7 +1067,7 @@ constexpr int kTicketSlots = 256;
 static __device__ unsigned int g_prefill_tickets[kTicketSlots];
 static std::atomic<unsigned int> g_next_ticket_slot{0};
 
-template <int D, bool PACKED = false>
+template <int D, int PACK = 1>
 static int launch_prefill_bounded(const CUtensorMap& mq, const CUtensorMap& mk,
                                   const CUtensorMap& mv, const CUtensorMap& mo, PrefillParams p,
                                   int B, cudaStream_t st) {
@@ -1081,7 +1081,7 @@ static int launch_prefill_bounded(const CUtensorMap& mq, const CUtensorMap& mk,
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_dev != dev) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_bounded_kernel<D, PACKED>,
+    cudaError_t e = cudaFuncSetAttribute(prefill_bounded_kernel<D, PACK>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
     if (e == cudaSuccess)
@@ -1093,10 +1093,10 @@ static int launch_prefill_bounded(const CUtensorMap& mq, const CUtensorMap& mk,
     }
     configured_dev = dev;
   }
-  // Packed layout: the query rows are walked in chunks of 32 (p.n_qtiles counts those) and an
+  // Packed layout: the query rows are walked in chunks of 128 / PACK (p.n_qtiles counts those) and an
   // item is a pair of chunks of one kv head, for all of its query heads at once.
-  const int heads = PACKED ? p.Hq / p.group : p.Hq;
-  if (PACKED) p.n_qtiles = (p.Sq + 31) / 32;
+  const int heads = PACK > 1 ? p.Hq / p.group : p.Hq;
+  if (PACK > 1) p.n_qtiles = (p.Sq + kTileQ / PACK - 1) / (kTileQ / PACK);
   p.n_pairs = (p.n_qtiles + 1) / 2;
   p.n_deferred = (p.mask_kind == LF_MASK_CAUSAL && p.Sq == p.Skv) ? p.n_pairs / 4 : 0;
   p.main_items = static_cast<int32_t>(static_cast<int64_t>(p.n_pairs - p.n_deferred) * heads * B);
@@ -1115,7 +1115,7 @@ static int launch_prefill_bounded(const CUtensorMap& mq, const CUtensorMap& mk,
   }
   const int ctas = sm_count - p.sm_margin > 0 ? sm_count - p.sm_margin : 1;
   const int grid = static_cast<int>(n_items < ctas ? n_items : ctas);
-  prefill_bounded_kernel<D, PACKED><<<grid, kBoundedThreads, smem, st>>>(mq, mk, mv, mo, p);
+  prefill_bounded_kernel<D, PACK><<<grid, kBoundedThreads, smem, st>>>(mq, mk, mv, mo, p);
   return check_launch("prefill_bounded_kernel");
 }
 
@@ -1330,15 +1330,15 @@ static int prefill_impl(const LfPrefillArgs* a, void* const* launch, int* q_tile
   }
   const int kv_tile = choose_kv_tile(a, mode);
   if (kv_tile < 0) return kv_tile;
-  // Four query heads per kv head under a window mask: the packed layout of the fixed-reference
-  // kernel (32 query rows of each of the four heads per tile slot).
-  const bool packed = mode == kModeBounded && kv_tile != kWideK && p.group == 4 &&
-                      a->mask_kind == LF_MASK_CAUSAL_WINDOW;
-  if (q_tile) *q_tile = packed ? 32 : kTileQ;
+  // Two or four query heads per kv head under a window mask: the packed layout of the
+  // fixed-reference kernel (128 / group query rows of each of the heads per tile slot).
+  const int pack = (mode == kModeBounded && kv_tile != kWideK && (p.group == 2 || p.group == 4) &&
+                    a->mask_kind == LF_MASK_CAUSAL_WINDOW) ? p.group : 1;
+  if (q_tile) *q_tile = kTileQ / pack;
   if (launch == nullptr) return kv_tile;  // query only
 
   CUtensorMap mq, mk, mv;
-  int rc = make_tile_map(&mq, a->q, a->B, a->Hq, a->Sq, a->D, a->q_stride, packed ? 32 : kTileQ);
+  int rc = make_tile_map(&mq, a->q, a->B, a->Hq, a->Sq, a->D, a->q_stride, kTileQ / pack);
   if (rc != LF_OK) return rc;
   if (p.paged & 1) {
     mk = mq;  // never used: the producer warp gathers K itself
@@ -1376,7 +1376,8 @@ static int prefill_impl(const LfPrefillArgs* a, void* const* launch, int* q_tile
     if (mode == kModeSoftcap) return launch_prefill<128, kModeSoftcap>(mq, mk, mv, p, a->B, st);
     if (mode == kModeBounded)
       return kv_tile == kWideK ? launch_prefill_wide<128>(mq, mk, mv, mo, p, a->B, st)
-             : packed          ? launch_prefill_bounded<128, true>(mq, mk, mv, mo, p, a->B, st)
+             : pack == 4       ? launch_prefill_bounded<128, 4>(mq, mk, mv, mo, p, a->B, st)
+             : pack == 2       ? launch_prefill_bounded<128, 2>(mq, mk, mv, mo, p, a->B, st)
                                : launch_prefill_bounded<128>(mq, mk, mv, mo, p, a->B, st);
     return launch_prefill<128, kModeGeneric>(mq, mk, mv, p, a->B, st);
   }
@@ -1384,7 +1385,8 @@ static int prefill_impl(const LfPrefillArgs* a, void* const* launch, int* q_tile
   if (mode == kModeSoftcap) return launch_prefill<64, kModeSoftcap>(mq, mk, mv, p, a->B, st);
   if (mode == kModeBounded)
     return kv_tile == kWideK ? launch_prefill_wide<64>(mq, mk, mv, mo, p, a->B, st)
-           : packed          ? launch_prefill_bounded<64, true>(mq, mk, mv, mo, p, a->B, st)
+           : pack == 4       ? launch_prefill_bounded<64, 4>(mq, mk, mv, mo, p, a->B, st)
+           : pack == 2       ? launch_prefill_bounded<64, 2>(mq, mk, mv, mo, p, a->B, st)
                              : launch_prefill_bounded<64>(mq, mk, mv, mo, p, a->B, st);
   return launch_prefill<64, kModeGeneric>(mq, mk, mv, p, a->B, st);
 }

@@ -119,13 +119,14 @@ __device__ __forceinline__ ItemGeom decode_item(const PrefillParams& p, int it,
   return g;
 }
 
-// PACKED (grouped-query attention with four query heads per kv head under a window mask): a
-// tile slot holds 32 query rows of each of the four heads instead of 128 rows of one head. The
-// keys a slot needs then span 32 + window - 1 positions instead of 128 + window - 1 (five 64-key
-// blocks instead of six at a window of 256, and six ring stages per item instead of eight), and
-// the four heads share every K/V tile in shared memory, not just in L2. Row r of a slot is row
-// r % 32 of the chunk for head h0 + r / 32: tensor-memory lane quadrant q is head h0 + q.
-template <int D, bool PACKED>
+// PACK (grouped-query attention with PACK = 2 or 4 query heads per kv head under a window
+// mask; 1 = one head per tile): a tile slot holds 128 / PACK query rows of each of the PACK heads
+// instead of 128 rows of one head. The keys a slot needs then span 128 / PACK + window - 1
+// positions instead of 128 + window - 1 (at PACK = 4 and a window of 256: five 64-key blocks
+// instead of six, and six ring stages per item instead of eight), and the heads share every K/V
+// tile in shared memory, not just in L2. Tensor-memory lane quadrant q (32 rows) belongs to
+// head h0 + q * PACK / 4 and holds rows (q % (4 / PACK)) * 32 .. + 32 of the slot's chunk.
+template <int D, int PACK>
 __global__ void __launch_bounds__(kBoundedThreads, 1)
     prefill_bounded_kernel(const __grid_constant__ CUtensorMap tmap_q,
                            const __grid_constant__ CUtensorMap tmap_k,
@@ -133,7 +134,9 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
                            const __grid_constant__ CUtensorMap tmap_o, const PrefillParams p) {
   constexpr int kStages = StagesFor<D>::value;
   constexpr int kBlocksD = D / 64;
-  constexpr int kRowsQ = PACKED ? 32 : kTileQ;  // query rows of a slot per head
+  static_assert(PACK == 1 || PACK == 2 || PACK == 4, "heads per tile");
+  constexpr bool PACKED = PACK > 1;
+  constexpr int kRowsQ = kTileQ / PACK;  // query rows of a slot per head
   constexpr uint32_t kQBlockBytes = kTileQ * 128;
   constexpr uint32_t kQTileBytes = kQBlockBytes * kBlocksD;
   constexpr uint32_t kKVBlockBytes = kTileK * 128;
@@ -286,13 +289,14 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
           ++qseq[t];
           if (elected) {
             mbar_arrive_expect_tx(&bars->q_full[t], kQTileBytes);
-            if constexpr (PACKED) {  // four boxes of 32 rows (one per head) per 64-column block
+            if constexpr (PACKED) {  // PACK boxes of kRowsQ rows (one per head) per 64-column block
 #pragma unroll
-              for (int hq = 0; hq < 4; ++hq)
+              for (int hq = 0; hq < PACK; ++hq)
 #pragma unroll
                 for (int kb = 0; kb < kBlocksD; ++kb)
-                  tma_load_4d(sQ + t * kQTileBytes + kb * kQBlockBytes + hq * (32 * 128), &tmap_q,
-                              &bars->q_full[t], kb * 64, (g.iq0 + t) * 32, g.h + hq, g.b);
+                  tma_load_4d(sQ + t * kQTileBytes + kb * kQBlockBytes + hq * (kRowsQ * 128),
+                              &tmap_q, &bars->q_full[t], kb * 64, (g.iq0 + t) * kRowsQ,
+                              g.h + hq, g.b);
             } else {
 #pragma unroll
               for (int kb = 0; kb < kBlocksD; ++kb)
@@ -488,9 +492,11 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
     for (int seq = 0; ok; ++seq) {
       const ItemGeom g = next_item(seq, true);
       if (g.it < 0) break;
-      const int grow = (g.iq0 + t) * kRowsQ + (PACKED ? lane : row);
-      const int head = PACKED ? g.h + quarter : g.h;
-      if (p.dbg_ranges && g.valid(t) && (PACKED ? lane : row) == 0 && half == 0) {
+      // row of this thread inside its head's chunk, and that head
+      const int crow = (quarter % (4 / PACK)) * 32 + lane;
+      const int grow = (g.iq0 + t) * kRowsQ + crow;
+      const int head = g.h + quarter * PACK / 4;
+      if (p.dbg_ranges && g.valid(t) && crow == 0 && half == 0) {
         const int64_t idx =
             ((static_cast<int64_t>(g.b) * p.Hq + head) * p.n_qtiles + (g.iq0 + t)) * 2;
         p.dbg_ranges[idx] = g.lo_t(t);
@@ -649,7 +655,7 @@ __global__ void __launch_bounds__(kBoundedThreads, 1)
       tc_fence_after();
       const float inv = 1.f / l_run;
       // first global row of the warp
-      const int row0 = PACKED ? (g.iq0 + t) * 32 : (g.iq0 + t) * kTileQ + quarter * 32;
+      const int row0 = (g.iq0 + t) * kRowsQ + (quarter % (4 / PACK)) * 32;
       // The warp's 32 rows x 32 columns go to its staging buffer in the 64-byte swizzle of the
       // output tensor map (16-byte piece q of row r at position q ^ ((r >> 1) & 3), conflict
       // free), and one bulk tensor store moves them to global memory; rows past Sq are clipped

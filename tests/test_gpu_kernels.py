@@ -341,13 +341,14 @@ def test_prefill_softcap_head_dim_64(S_, W, kv_tile):
     assert max_err(out, want) <= TOL
 
 
+@pytest.mark.parametrize("G", [2, 4])
 @pytest.mark.parametrize("S_,W", [(1024, 200), (333, 96)])
-def test_prefill_packed_gqa_layout_head_dim_64(S_, W):
-    """Four query heads per kv head under a window mask at D = 64: the packed layout (32 rows of
-    each head per tile), ragged sizes, more than one kv head and batch."""
-    q, k, v = _prefill_case(2, 8, 2, S_, S_, 64, scale=1.5)
+def test_prefill_packed_gqa_layout_head_dim_64(S_, W, G):
+    """Two or four query heads per kv head under a window mask at D = 64: the packed layout
+    (128 / G rows of each head per tile), ragged sizes, more than one kv head and batch."""
+    q, k, v = _prefill_case(2, 2 * G, 2, S_, S_, 64, scale=1.5)
     kw = dict(scale=64 ** -0.5, mods=SOFTCAP, mask_kind=S.MASK_CAUSAL_WINDOW, window=W)
-    assert F.prefill_q_tile(q.to(DEV), k.to(DEV), v.to(DEV), **kw) == 32
+    assert F.prefill_q_tile(q.to(DEV), k.to(DEV), v.to(DEV), **kw) == 128 // G
     out = _run_prefill(q, k, v, **kw)
     want = O.attention_ref(q, k, v, mods=O.softcap_mods(50.0), mask="window", window=W,
                            batch_chunk=2)
