@@ -1073,8 +1073,11 @@ static int launch_prefill_bounded(const CUtensorMap& mq, const CUtensorMap& mk,
                                   int B, cudaStream_t st) {
   constexpr size_t kQTileBytes = static_cast<size_t>(kTileQ) * D * 2;
   constexpr size_t kKVTileBytes = static_cast<size_t>(kTileK) * D * 2;
-  constexpr size_t smem = 1024 /*align slack*/ + 1024 /*barriers*/ + kBoundedStageBytes +
-                          2 * kQTileBytes + StagesFor<D>::value * 2 * kKVTileBytes;
+  constexpr bool kBig = PACK > 1 && D == 128;
+  constexpr size_t smem = 1024 /*align slack*/ + 1024 /*barriers*/ +
+                          (kBig ? 16 * 4096 : kBoundedStageBytes) + 2 * kQTileBytes +
+                          (kBig ? 3 : StagesFor<D>::value) * 2 * kKVTileBytes;
+  static_assert(smem <= 232448, "smem");
   static thread_local int configured_dev = -1;
   static thread_local unsigned int* tickets = nullptr;
   static thread_local int sm_count = 0;
@@ -1355,7 +1358,8 @@ static int prefill_impl(const LfPrefillArgs* a, void* const* launch, int* q_tile
 
   CUtensorMap mo;  // output store boxes of the persistent kernels: 32 rows x 32 columns
   if (mode == kModeBounded) {
-    rc = make_tile_map(&mo, a->out, a->B, a->Hq, a->Sq, a->D, a->o_stride, 32, 32);
+    rc = make_tile_map(&mo, a->out, a->B, a->Hq, a->Sq, a->D, a->o_stride, 32,
+                       (pack > 1 && a->D == 128) ? 64 : 32);
     if (rc != LF_OK) return rc;
   }
 
