@@ -53,7 +53,7 @@ METRIC = "prefill TFLOP/s (causal-adjusted FLOPs) per job; decode HBM GB/s under
 # traffic is proportional to the batch).
 NCU_TRAFFIC_BYTES = {
     "causal_softcap": 4 * (108.67e6 + 14.64e6),
-    "window_gqa_softcap": 2 * (100.74e6 + 32.34e6),
+    "window_gqa_softcap": 2 * (100.74e6 + 30.84e6),
     "decode": 8 * (268.51e6 + 4.03e6),
     "paged_decode_gqa": 2 * (268.79e6 + 5.29e6),
 }
